@@ -15,6 +15,7 @@ from typing import Any, Callable, Mapping
 
 from tinyserve_llm_b200.config.duduvik import DuduvikConfig, duduvik_model_spec
 from tinyserve_llm_b200.config.llama import ConfigError, LlamaConfig, llama_model_spec
+from tinyserve_llm_b200.config.lugipel import LugipelConfig, lugipel_model_spec
 from tinyserve_llm_b200.config.nipizen import NipizenConfig, nipizen_model_spec
 from tinyserve_llm_b200.config.spec import ModelSpec
 
@@ -38,6 +39,7 @@ def register_architecture(arch: Architecture) -> Architecture:
 register_architecture(Architecture("LlamaForCausalLM", "llama", LlamaConfig.from_dict, llama_model_spec))
 register_architecture(Architecture("Duduvik", "duduvik", DuduvikConfig.from_dict, duduvik_model_spec))
 register_architecture(Architecture("Nipizen", "nipizen", NipizenConfig.from_dict, nipizen_model_spec))
+register_architecture(Architecture("Lugipel", "lugipel", LugipelConfig.from_dict, lugipel_model_spec))
 
 
 def resolve_architecture(raw: Mapping[str, Any]) -> Architecture:

@@ -156,6 +156,34 @@ class AttentionSpec(PartSpec):
 
 
 @dataclass(frozen=True)
+class SinusoidSpec(PartSpec):
+    """
+    A position vector added to the token embedding as it starts the residual stream: with
+    angle_i = position * base^(-2i/size), entry 2i is sin(angle_i) and entry 2i + 1 cos(angle_i).
+    Angles are computed in float32 inside the kernel that gathers the embedding rows (no table).
+    """
+
+    kind: str = field(init=False, default="sinusoid")
+    size: int = 0
+    base: float = 10000.0
+
+
+@dataclass(frozen=True)
+class MinGRUSpec(PartSpec):
+    """
+    Element-wise gated recurrence whose gates read the current token only (a minGRU), `width` channels:
+    z = sigmoid(W_z h + b_z), u = W_x h + b_x, c = u + 1/2 where u >= 0 and sigmoid(u) below,
+    S_t = (1 - z) S_(t-1) + z c, y = W_o (S_t * silu(W_g h)).  The state (float32, one number a channel
+    and request) starts at zero.  `bias`: the tensors `z.b` and `x.b` exist.
+    """
+
+    kind: str = field(init=False, default="mingru")
+    hidden_size: int = 0
+    width: int = 0
+    bias: bool = True
+
+
+@dataclass(frozen=True)
 class StreamLayerNormSpec(PartSpec):
     """
     Layer norm with a weight and no bias, (x - mean) / sqrt(mean((x - mean)^2) + eps) * w, beside a
@@ -176,6 +204,14 @@ class GatedAttentionSpec(PartSpec):
     optional biases on q, k, v (tensor name + ".b"), an optional RMS norm of q and of k over the whole
     projection (all heads at once, plain weights `q.norm`, `k.norm`) before the rotation, and an
     optional output gate sigmoid(W_g h) on the concatenated heads before the output projection.
+
+    Further options, each off by default: `qk_norm_scope` "head" norms every head of q and of k by
+    itself with one weight of head_dim elements shared by the heads; `q_temperature_every` > 0
+    multiplies q by 1 + q_temperature_coef * ln(floor((position + 1) / every) + 1);
+    `distance_slope_exponent` c > 0 takes slope_h * (i - j) off the score of query i and key j,
+    slope_h = 2^(-c (h + 1) / num_heads); `head_bias` adds the number `pb`[h] to every score of head h;
+    `weights` "sigmoid" makes a visible key's weight sigmoid(score) without any normalisation over
+    the keys; `output_gate_scope` "head" gates with one number a head (`g` is [num_heads, hidden]).
     """
 
     kind: str = field(init=False, default="gated_attention")
@@ -191,6 +227,13 @@ class GatedAttentionSpec(PartSpec):
     qk_norm_eps: float = 1e-6
     output_gate: bool = False
     position: PartSpec | None = None
+    qk_norm_scope: str = "projection"    # "projection": one norm over all heads' channels; "head": one a head
+    q_temperature_coef: float = 0.0
+    q_temperature_every: int = 0         # 0: no query temperature
+    distance_slope_exponent: float = 0.0  # 0: no distance penalty
+    head_bias: bool = False
+    weights: str = "softmax"             # "softmax" over the visible keys, or "sigmoid" of each score
+    output_gate_scope: str = "channel"   # "channel": a gate a value channel; "head": one a head
 
 
 @dataclass(frozen=True)
@@ -254,13 +297,18 @@ class ParallelMixerSpec(PartSpec):
 
 @dataclass(frozen=True)
 class PlainMLPSpec(PartSpec):
-    """Ungated feed-forward down(act(up(x))); `activation` "relu2" is the square of relu."""
+    """
+    Ungated feed-forward down(act(up(x))); `activation` "relu2" is the square of relu; "xielu" is
+    softplus(p) z^2 + z/2 for z > 0 and (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2 for z <= 0 with the
+    two numbers p, q of the tensor `param_name`.
+    """
 
     kind: str = field(init=False, default="plain_mlp")
     hidden_size: int = 0
     intermediate_size: int = 0
     activation: str = "relu2"
     tensor_names: tuple[str, str] = ("up", "down")
+    param_name: str | None = None        # the activation's own numbers, where it has some
 
 
 @dataclass(frozen=True)
@@ -297,10 +345,21 @@ class RoutedExpertsSpec(PartSpec):
     shared_prefix: str = "shared."
     router_name: str = "router"
     router_bias_name: str | None = "router.b"
-    # "softmax_chosen": softmax over the chosen logits; "sigmoid": each chosen expert's sigmoid(logit), not renormalised
+    # "softmax_chosen": softmax over the chosen logits; "sigmoid": each chosen expert's sigmoid(logit), not renormalised;
+    # "softmax_all": scores are the softmax over ALL router outputs; the choice is made by score + `correction_name`
+    # (a tensor, optional) among the experts of the `group_keep` best of `group_count` groups of neighbours (a group's
+    # rank is its largest choice score); the weights are the chosen scores (without the correction) divided by
+    # their sum + `share_eps`, times `weight_scale`
     scoring: str = "softmax_chosen"
     # "output": the weight multiplies the expert's output; "input": its input (experts without a gate only)
     weight_on: str = "output"
+    correction_name: str | None = None
+    group_count: int = 1
+    group_keep: int = 1
+    weight_scale: float = 1.0
+    share_eps: float = 0.0
+    # the router's last `identity_experts` outputs stand for experts without tensors whose output is their input
+    identity_experts: int = 0
 
 
 @dataclass(frozen=True)
@@ -361,6 +420,7 @@ class ModelSpec:
     ignored_suffixes: tuple[str, ...] = ()     # tensors whose names end so are skipped (buffers the model recomputes)
     extras: dict[str, Any] = field(default_factory=dict, compare=False)
     embedding_scale: float = 1.0               # multiplies the embedding rows as they start the stream (not the tied head)
+    embedding_position: PartSpec | None = None  # a position vector added to the scaled embedding rows (`SinusoidSpec`)
 
     @property
     def num_cache_entries(self) -> int:

@@ -67,3 +67,43 @@ TS_API int ts_silu_mul(const void* gate_up, void* out, int num_tokens, int inter
     TS_LAUNCH_CHECK("silu_mul");
     return 0;
 }
+
+// out[i] = act(x[i]) for the activations of one argument (common.cuh); 16 bytes a thread where the pointers allow.
+template <typename T, bool VEC>
+__global__ void unary_activation_kernel(const T* __restrict__ x, T* __restrict__ out, long long total, int kind, float a,
+                                        float b) {
+    constexpr int VN = VEC ? 16 / (int)sizeof(T) : 1;
+    for (long long idx = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * VN; idx < total;
+         idx += (long long)gridDim.x * blockDim.x * VN) {
+        if (VEC) {
+            uint4 raw = *reinterpret_cast<const uint4*>(x + idx);
+            T* v = reinterpret_cast<T*>(&raw);
+#pragma unroll
+            for (int i = 0; i < VN; ++i) v[i] = from_float<T>(ts_unary_activation(kind, to_float<T>(v[i]), a, b));
+            *reinterpret_cast<uint4*>(out + idx) = raw;
+        } else {
+            out[idx] = from_float<T>(ts_unary_activation(kind, to_float<T>(x[idx]), a, b));
+        }
+    }
+}
+
+TS_API int ts_unary_activation_rows(const void* x, void* out, long long total, int kind, float a, float b, int dtype,
+                                    cudaStream_t stream) {
+    TS_REQUIRE(total >= 0 && (kind == TS_UNARY_RELU2 || kind == TS_UNARY_XIELU), "unary_activation: bad arguments");
+    if (total == 0) return 0;
+    const int vn = dtype == TS_F32 ? 4 : 8;
+    const bool vec = total % vn == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0;
+    const long long threads = vec ? total / vn : total;
+    const unsigned blocks = (unsigned)((threads + 255) / 256 < 148 * 16 ? (threads + 255) / 256 : 148 * 16);
+#define TS_UNARY(TYPE)                                                                                                   \
+    do {                                                                                                                 \
+        if (vec) unary_activation_kernel<TYPE, true><<<blocks, 256, 0, stream>>>((const TYPE*)x, (TYPE*)out, total, kind, a, b);  \
+        else unary_activation_kernel<TYPE, false><<<blocks, 256, 0, stream>>>((const TYPE*)x, (TYPE*)out, total, kind, a, b);     \
+    } while (0)
+    if (dtype == TS_F32) TS_UNARY(float);
+    else if (dtype == TS_BF16) TS_UNARY(__nv_bfloat16);
+    else return ts_fail("unary_activation: unknown dtype code %d", dtype);
+#undef TS_UNARY
+    TS_LAUNCH_CHECK("unary_activation");
+    return 0;
+}

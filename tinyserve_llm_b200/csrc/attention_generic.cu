@@ -10,7 +10,19 @@
 // maximum, sum and output; lanes merge at the end.  The order of every sum depends only on the
 // query's position, never on how the step was cut or what else is in the batch.  Softmax and both
 // products accumulate in float32.
+//
+// Options of the score and of the weights (`AttentionExtras`), for designs that have them:
+//   score(i, j) = q_i . k_j * scale - slopes[h] * (i - j) + head_bias[h]      (each term optional)
+//   SIGMOID: the weight of a visible key is sigmoid(score), with no normalisation over the keys
+//   gate: head h's output is multiplied by sigmoid(gate[t, h]) (one logit a token and head)
 #include "common.cuh"
+
+struct AttentionExtras {
+    const float* slopes;       // [nh] or null
+    const float* head_bias;    // [nh] or null
+    const void* gate;          // [tokens, nh] logits in the activation dtype, `gate_stride` elements a row, or null
+    long long gate_stride;
+};
 
 template <typename T>
 struct Vec16;   // 16 bytes of T
@@ -40,13 +52,13 @@ __device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* p, fl
 constexpr int WARPS = 4;
 
 // queries: row t of `q` (`q_stride` elements a row), head h at h * hd; output [tokens, nh * vd]
-template <typename T, int MAXHD, bool VEC>
+template <typename T, int MAXHD, bool VEC, bool SIGMOID>
 __global__ void __launch_bounds__(WARPS * 32)
 paged_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__ out,
                                const T* __restrict__ k_pool, const T* __restrict__ v_pool, KVGeometry geo, KVGeometry geo_v,
                                const int* __restrict__ block_table, int table_width, const int* __restrict__ positions,
                                const int* __restrict__ seq_of_token, int num_tokens, int nh, int nkv, int hd, int vd,
-                               float scale, int window) {
+                               float scale, int window, AttentionExtras extras) {
     __shared__ float q_smem[WARPS][MAXHD];
     constexpr int VN = Vec16<T>::N;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -66,6 +78,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* _
 #pragma unroll
     for (int d = 0; d < MAXHD; ++d) o[d] = 0.f;
     float m = -INFINITY, l = 0.f;
+    const float slope = extras.slopes ? extras.slopes[h] : 0.f;
+    const float bias = extras.head_bias ? extras.head_bias[h] : 0.f;
 
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const long long head_off = geo.entry_offset + (long long)kvh * geo.page_tokens * hd;
@@ -91,15 +105,21 @@ paged_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* _
 #pragma unroll 4
             for (int d = 0; d < hd; ++d) s = fmaf(q_smem[warp][d], to_float<T>(kp[d]), s);
         }
-        if (s > m) {
-            const float c = expf(m - s);                       // 0 on the first key (m = -inf)
-            l *= c;
+        s = s - slope * (float)(pos - j) + bias;
+        float p;
+        if (SIGMOID) {
+            p = 1.f / (1.f + expf(-s));
+        } else {
+            if (s > m) {
+                const float c = expf(m - s);                   // 0 on the first key (m = -inf)
+                l *= c;
 #pragma unroll
-            for (int d = 0; d < MAXHD; ++d) o[d] *= c;
-            m = s;
+                for (int d = 0; d < MAXHD; ++d) o[d] *= c;
+                m = s;
+            }
+            p = expf(s - m);
+            l += p;
         }
-        const float p = expf(s - m);
-        l += p;
         const T* vp = v_pool + (long long)page * geo_v.page_stride + head_off_v + (long long)(j % geo.page_tokens) * vd;
         if (VEC) {
 #pragma unroll
@@ -118,10 +138,15 @@ paged_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* _
         }
     }
     // merge the lanes
-    const float m_all = warp_max(m);
-    const float f = (m == -INFINITY) ? 0.f : expf(m - m_all);
-    const float l_all = warp_sum(l * f);
-    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+    float f = 1.f, inv = 1.f;
+    if (!SIGMOID) {
+        const float m_all = warp_max(m);
+        f = (m == -INFINITY) ? 0.f : expf(m - m_all);
+        const float l_all = warp_sum(l * f);
+        inv = l_all > 0.f ? 1.f / l_all : 0.f;
+    }
+    if (extras.gate)
+        inv /= 1.f + expf(-to_float<T>(((const T*)extras.gate)[(long long)t * extras.gate_stride + h]));
 #pragma unroll
     for (int d = 0; d < MAXHD; ++d) {
         if (d < vd) {
@@ -135,7 +160,7 @@ template <typename T, int MAXHD>
 static int launch(const void* q, long long q_stride, void* out, const void* k_pool, const void* v_pool, KVGeometry geo,
                   KVGeometry geo_v, const int* block_table, int table_width, const int* positions,
                   const int* seq_of_token, int num_tokens, int nh, int nkv, int hd, int vd, float scale, int window,
-                  cudaStream_t stream) {
+                  int sigmoid, AttentionExtras extras, cudaStream_t stream) {
     const long long items = (long long)num_tokens * nh;
     const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
     const int vn = Vec16<T>::N;
@@ -143,25 +168,29 @@ static int launch(const void* q, long long q_stride, void* out, const void* k_po
     const bool vec = hd % vn == 0 && vd % vn == 0 && geo.page_stride % vn == 0 && geo.entry_offset % vn == 0 &&
                      geo_v.page_stride % vn == 0 && geo_v.entry_offset % vn == 0 && (uintptr_t)k_pool % 16 == 0 &&
                      (uintptr_t)v_pool % 16 == 0;
-    if (vec)
-        paged_attention_generic_kernel<T, MAXHD, true><<<blocks, WARPS * 32, 0, stream>>>(
-            (const T*)q, q_stride, (T*)out, (const T*)k_pool, (const T*)v_pool, geo, geo_v, block_table, table_width,
-            positions, seq_of_token, num_tokens, nh, nkv, hd, vd, scale, window);
-    else
-        paged_attention_generic_kernel<T, MAXHD, false><<<blocks, WARPS * 32, 0, stream>>>(
-            (const T*)q, q_stride, (T*)out, (const T*)k_pool, (const T*)v_pool, geo, geo_v, block_table, table_width,
-            positions, seq_of_token, num_tokens, nh, nkv, hd, vd, scale, window);
+#define TS_ATTENTION_LAUNCH(V, S)                                                                                   \
+    paged_attention_generic_kernel<T, MAXHD, V, S><<<blocks, WARPS * 32, 0, stream>>>(                              \
+        (const T*)q, q_stride, (T*)out, (const T*)k_pool, (const T*)v_pool, geo, geo_v, block_table, table_width,   \
+        positions, seq_of_token, num_tokens, nh, nkv, hd, vd, scale, window, extras)
+    if (vec && sigmoid) TS_ATTENTION_LAUNCH(true, true);
+    else if (vec) TS_ATTENTION_LAUNCH(true, false);
+    else if (sigmoid) TS_ATTENTION_LAUNCH(false, true);
+    else TS_ATTENTION_LAUNCH(false, false);
+#undef TS_ATTENTION_LAUNCH
     TS_LAUNCH_CHECK("paged_attention_generic");
     return 0;
 }
 
-// Queries in a tensor of their own, values of head size `vd` in a pool with a geometry of its own.
-TS_API int ts_paged_attention_split(const void* q, long long q_stride, void* out, const void* k_pool, const void* v_pool,
-                                    long long page_stride, long long entry_offset, long long v_page_stride,
-                                    long long v_entry_offset, int page_tokens, int num_pages, const int* block_table,
-                                    int table_width, const int* positions, const int* seq_of_token, int num_tokens,
-                                    int nh, int nkv, int hd, int vd, float scale, int window, int dtype,
-                                    cudaStream_t stream) {
+// Queries in a tensor of their own, values of head size `vd` in a pool with a geometry of its own; the options of
+// the score and of the weights as arguments (`sigmoid` 1: sigmoid weights; null pointers: the term is absent).
+TS_API int ts_paged_attention_scored(const void* q, long long q_stride, void* out, const void* k_pool, const void* v_pool,
+                                     long long page_stride, long long entry_offset, long long v_page_stride,
+                                     long long v_entry_offset, int page_tokens, int num_pages, const int* block_table,
+                                     int table_width, const int* positions, const int* seq_of_token, int num_tokens,
+                                     int nh, int nkv, int hd, int vd, float scale, int window, int dtype, int sigmoid,
+                                     const float* slopes, const float* head_bias, const void* gate, long long gate_stride,
+                                     cudaStream_t stream) {
+    const AttentionExtras extras{slopes, head_bias, gate, gate_stride};
     TS_REQUIRE(num_tokens >= 0 && nh > 0 && nkv > 0, "paged_attention: bad sizes");
     TS_REQUIRE(nh % nkv == 0, "paged_attention: %d query heads are not a multiple of %d kv heads", nh, nkv);
     TS_REQUIRE(hd > 0 && hd <= 256 && vd > 0 && vd <= 256,
@@ -173,17 +202,30 @@ TS_API int ts_paged_attention_split(const void* q, long long q_stride, void* out
     const int widest = hd > vd ? hd : vd;
 #define TS_DISPATCH(TYPE)                                                                                          \
     if (widest <= 32) return launch<TYPE, 32>(q, q_stride, out, k_pool, v_pool, geo, geo_v, block_table, table_width, \
-                                              positions, seq_of_token, num_tokens, nh, nkv, hd, vd, scale, window, stream); \
+                                              positions, seq_of_token, num_tokens, nh, nkv, hd, vd, scale, window, sigmoid, extras, stream); \
     if (widest <= 64) return launch<TYPE, 64>(q, q_stride, out, k_pool, v_pool, geo, geo_v, block_table, table_width, \
-                                              positions, seq_of_token, num_tokens, nh, nkv, hd, vd, scale, window, stream); \
+                                              positions, seq_of_token, num_tokens, nh, nkv, hd, vd, scale, window, sigmoid, extras, stream); \
     if (widest <= 128) return launch<TYPE, 128>(q, q_stride, out, k_pool, v_pool, geo, geo_v, block_table, table_width, \
-                                                positions, seq_of_token, num_tokens, nh, nkv, hd, vd, scale, window, stream); \
+                                                positions, seq_of_token, num_tokens, nh, nkv, hd, vd, scale, window, sigmoid, extras, stream); \
     return launch<TYPE, 256>(q, q_stride, out, k_pool, v_pool, geo, geo_v, block_table, table_width, positions,      \
-                             seq_of_token, num_tokens, nh, nkv, hd, vd, scale, window, stream);
+                             seq_of_token, num_tokens, nh, nkv, hd, vd, scale, window, sigmoid, extras, stream);
     if (dtype == TS_F32) { TS_DISPATCH(float) }
     if (dtype == TS_BF16) { TS_DISPATCH(__nv_bfloat16) }
 #undef TS_DISPATCH
     return ts_fail("paged_attention: unknown dtype code %d", dtype);
+}
+
+// Softmax attention without further terms.
+TS_API int ts_paged_attention_split(const void* q, long long q_stride, void* out, const void* k_pool, const void* v_pool,
+                                    long long page_stride, long long entry_offset, long long v_page_stride,
+                                    long long v_entry_offset, int page_tokens, int num_pages, const int* block_table,
+                                    int table_width, const int* positions, const int* seq_of_token, int num_tokens,
+                                    int nh, int nkv, int hd, int vd, float scale, int window, int dtype,
+                                    cudaStream_t stream) {
+    return ts_paged_attention_scored(q, q_stride, out, k_pool, v_pool, page_stride, entry_offset, v_page_stride,
+                                     v_entry_offset, page_tokens, num_pages, block_table, table_width, positions,
+                                     seq_of_token, num_tokens, nh, nkv, hd, vd, scale, window, dtype, 0, nullptr, nullptr,
+                                     nullptr, 0, stream);
 }
 
 // Queries, keys and values of one head size in the columns [q | k | v] of one projection's output.

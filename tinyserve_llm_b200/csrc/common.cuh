@@ -66,6 +66,16 @@ __device__ __forceinline__ float ts_gated_activation(int kind, float g, float u,
     return g / (1.f + expf(-g)) * u;
 }
 
+// Activations of one argument, act(z) with two numbers a, b of the layer:  0: relu(z)^2;
+// 1 (xIELU): a z^2 + z/2 for z > 0, b (exp(z) - 1 - z) + z/2 for z <= 0 (the host gives a = softplus(p), b = 1/2 + softplus(q)).
+enum { TS_UNARY_RELU2 = 0, TS_UNARY_XIELU = 1 };
+
+__device__ __forceinline__ float ts_unary_activation(int kind, float z, float a, float b) {
+    if (kind == TS_UNARY_XIELU) return z > 0.f ? fmaf(a * z, z, 0.5f * z) : fmaf(b, expm1f(z) - z, 0.5f * z);
+    const float r = fmaxf(z, 0.f);
+    return r * r;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

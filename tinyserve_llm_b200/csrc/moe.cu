@@ -3,7 +3,13 @@
 //
 //   ts_moe_route     per token: the `top` largest router logits (float32, bias added here; ties go to
 //                    the lower index), their softmax, and a count per expert.  `scoring` 1: a chosen
-//                    expert's share is sigmoid(logit) instead, not renormalised.
+//                    expert's share is sigmoid(logit) instead, not renormalised.  `scoring` 2: scores are the
+//                    softmax over ALL router outputs; the choice goes by score + correction[e] among the
+//                    outputs of the `keep` best of `groups` equal groups of neighbours (a group ranks by its
+//                    largest choice score); a chosen output's share is its score (without the correction)
+//                    divided by the chosen scores' sum + share_eps, times weight_scale.  Outputs from
+//                    `real_experts` on are identity experts: they get no row in any expert's stretch
+//                    (chosen = -1) and their shares are added up in identity_share[t] for ts_moe_combine.
 //   ts_moe_arrange   (token, choice) pairs sorted by expert: every CTA takes the exclusive scan of the
 //                    counts and places its pairs behind their expert's offset.  Which row of an
 //                    expert's stretch a pair lands in is not fixed; no result depends on it.
@@ -18,7 +24,8 @@
 //                    A step of up to 64 pairs takes a weight-streaming kernel instead (further down); large
 //                    bfloat16 steps may be given to the library's grouped product by the caller.
 //   ts_moe_combine   out[t] = sum_j share[t, j] * y[row of (t, j)] (+ the shared expert's output), in the
-//                    order of j, float32, rounded once.  Without `share` every weight is 1.
+//                    order of j, float32, rounded once.  Without `share` every weight is 1.  With
+//                    `identity_share`, identity_share[t] * x[t] is added (the identity experts' part).
 #include "common.cuh"
 
 // the kinds of gated activation are those of common.cuh (ts_gated_activation)
@@ -73,6 +80,120 @@ TS_API int ts_moe_route(const float* logits, const float* bias, const int* seq_o
     moe_route_kernel<<<(num_tokens + 3) / 4, 128, 0, stream>>>(logits, bias, seq_of_token, chosen, share, counts,
                                                                num_tokens, experts, top, scoring);
     TS_LAUNCH_CHECK("moe_route");
+    return 0;
+}
+
+// Scores over all router outputs, choice inside the best groups (see the head of this file).  A warp a token;
+// every lane recomputes the scores it needs from the logits, so nothing but the groups' ranks is kept.
+__global__ void moe_route_grouped_kernel(const float* __restrict__ logits, const float* __restrict__ correction,
+                                         const int* __restrict__ seq_of_token, int* __restrict__ chosen,
+                                         float* __restrict__ share, int* __restrict__ counts, float* __restrict__ identity_share,
+                                         int num_tokens, int outputs, int real_experts, int top, int groups, int keep,
+                                         float weight_scale, float share_eps) {
+    extern __shared__ float group_rank[];                 // per warp: `groups` ranks, then `groups` flags (kept or not)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= num_tokens) return;
+    if (seq_of_token && seq_of_token[t] < 0) {            // a padding row takes part in nothing
+        for (int j = lane; j < top; j += 32) chosen[(long long)t * top + j] = -1;
+        if (lane == 0 && identity_share) identity_share[t] = 0.f;
+        return;
+    }
+    float* rank = group_rank + (size_t)warp * 2 * groups;
+    int* kept = reinterpret_cast<int*>(rank + groups);
+    const float* z = logits + (long long)t * outputs;
+    float zmax = -INFINITY;
+    for (int e = lane; e < outputs; e += 32) zmax = fmaxf(zmax, z[e]);
+    zmax = warp_max(zmax);
+    float sum = 0.f;
+    for (int e = lane; e < outputs; e += 32) sum += expf(z[e] - zmax);
+    const float inv_sum = 1.f / warp_sum(sum);
+    auto score = [&](int e) { return expf(z[e] - zmax) * inv_sum; };
+    auto choice = [&](int e) { return score(e) + (correction ? correction[e] : 0.f); };
+    const int per = outputs / groups;
+    if (keep < groups) {
+        for (int g = lane; g < groups; g += 32) {
+            float m = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) m = fmaxf(m, choice(e));
+            rank[g] = m;
+            kept[g] = 0;
+        }
+        __syncwarp();
+        for (int r = 0; r < keep; ++r) {                  // the best group not kept yet; ties go to the lower index
+            float best = -INFINITY;
+            int arg = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32) {
+                if (kept[g]) continue;
+                const float x = rank[g];
+                if (x > best || (x == best && g < arg)) { best = x; arg = g; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+                if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+            }
+            if (lane == 0 && arg != 0x7fffffff) kept[arg] = 1;
+            __syncwarp();
+        }
+    }
+    float total = 0.f, identity = 0.f;
+    unsigned long long taken_lo = 0;
+    for (int j = 0; j < top; ++j) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane, i = 0; e < outputs; e += 32, ++i) {
+            if (taken_lo >> i & 1) continue;
+            if (keep < groups && !kept[e / per]) continue;
+            const float x = choice(e);
+            if (x > best || (x == best && e < arg)) { best = x; arg = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (arg == 0x7fffffff) {                           // fewer outputs allowed than `top`: the choice stays empty
+            if (lane == 0) { chosen[(long long)t * top + j] = -1; share[(long long)t * top + j] = 0.f; }
+            continue;
+        }
+        if ((arg & 31) == lane) taken_lo |= 1ull << (arg >> 5);
+        const float w = score(arg);
+        total += w;
+        const bool real = arg < real_experts;
+        if (!real) identity += w;
+        if (lane == 0) {
+            chosen[(long long)t * top + j] = real ? arg : -1;
+            share[(long long)t * top + j] = w;
+            if (real) atomicAdd(counts + arg, 1);
+        }
+    }
+    __syncwarp();
+    const float norm = weight_scale / (total + share_eps);
+    if (lane == 0) {
+        for (int j = 0; j < top; ++j) share[(long long)t * top + j] *= norm;
+        if (identity_share) identity_share[t] = identity * norm;
+    }
+}
+
+TS_API int ts_moe_route_grouped(const float* logits, const float* correction, const int* seq_of_token, int* chosen,
+                                float* share, int* counts, float* identity_share, int num_tokens, int outputs,
+                                int real_experts, int top, int groups, int keep, float weight_scale, float share_eps,
+                                cudaStream_t stream) {
+    TS_REQUIRE(outputs > 0 && top > 0 && top <= outputs && real_experts >= 0 && real_experts <= outputs,
+               "moe_route: %d of %d router outputs, %d of them experts", top, outputs, real_experts);
+    TS_REQUIRE(outputs <= 2048, "moe_route: %d router outputs are not supported (up to 2048)", outputs);
+    TS_REQUIRE(groups > 0 && outputs % groups == 0 && keep > 0 && keep <= groups && groups <= 1024,
+               "moe_route: %d outputs in %d groups of which %d are kept", outputs, groups, keep);
+    TS_REQUIRE(real_experts == outputs || identity_share, "moe_route: identity experts need a place for their shares");
+    if (num_tokens <= 0) return 0;
+    const size_t smem = (size_t)4 * 2 * groups * sizeof(float);
+    moe_route_grouped_kernel<<<(num_tokens + 3) / 4, 128, smem, stream>>>(logits, correction, seq_of_token, chosen, share,
+                                                                        counts, identity_share, num_tokens, outputs,
+                                                                        real_experts, top, groups, keep, weight_scale,
+                                                                        share_eps);
+    TS_LAUNCH_CHECK("moe_route_grouped");
     return 0;
 }
 
@@ -372,7 +493,7 @@ TS_API int ts_moe_linear(const void* x, long long x_stride, const int* pair_of_r
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ row_of_pair,
                                    const float* __restrict__ share, const T* __restrict__ shared_out, T* __restrict__ out,
-                                   int width, int top) {
+                                   int width, int top, const T* __restrict__ x, const float* __restrict__ identity_share) {
     const long long t = blockIdx.x;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float s = 0.f;
@@ -381,19 +502,23 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restric
             if (row >= 0) s = fmaf(share ? share[t * top + j] : 1.f, to_float<T>(y[(long long)row * width + i]), s);
         }
         if (shared_out) s += to_float<T>(shared_out[t * width + i]);
+        if (identity_share) s = fmaf(identity_share[t], to_float<T>(x[t * width + i]), s);
         out[t * width + i] = from_float<T>(s);
     }
 }
 
 TS_API int ts_moe_combine(const void* y, const int* row_of_pair, const float* share, const void* shared_out, void* out,
-                          int num_tokens, int width, int top, int dtype, cudaStream_t stream) {
+                          int num_tokens, int width, int top, int dtype, const void* x, const float* identity_share,
+                          cudaStream_t stream) {
+    TS_REQUIRE(!identity_share || x, "moe_combine: identity experts need the experts' input");
     if (num_tokens <= 0) return 0;
     if (dtype == TS_F32)
         moe_combine_kernel<float><<<num_tokens, 128, 0, stream>>>((const float*)y, row_of_pair, share,
-                                                                  (const float*)shared_out, (float*)out, width, top);
+                                                                  (const float*)shared_out, (float*)out, width, top,
+                                                                  (const float*)x, identity_share);
     else if (dtype == TS_BF16)
         moe_combine_kernel<__nv_bfloat16><<<num_tokens, 128, 0, stream>>>((const __nv_bfloat16*)y, row_of_pair, share,
-            (const __nv_bfloat16*)shared_out, (__nv_bfloat16*)out, width, top);
+            (const __nv_bfloat16*)shared_out, (__nv_bfloat16*)out, width, top, (const __nv_bfloat16*)x, identity_share);
     else
         return ts_fail("moe_combine: unknown dtype code %d", dtype);
     TS_LAUNCH_CHECK("moe_combine");

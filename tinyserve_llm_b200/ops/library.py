@@ -50,7 +50,7 @@ _SIGNATURES = {
     "ts_skinny_qkv_rope_store": ("int", "pppiilpppiipipplliiiiiip"),
     "ts_skinny_linear_gated": ("int", "pppiiilliffp"),
     "ts_gemm_tcgen05_gated": ("int", "pppiiilliffpp"),
-    "ts_stream_norm": ("int", "ppppppiifppifiip"),
+    "ts_stream_norm": ("int", "ppppppiifppifiippp"),
     "ts_linear_recurrence": ("int", "ppplllplppfffpipppiplpiiiipip"),
     "ts_head_norm_gate": ("int", "piplpippliiififip"),
     "ts_latent_prepare": ("int", "pliiippfppppplliipiiiip"),
@@ -60,10 +60,14 @@ _SIGNATURES = {
     "ts_moe_route": ("int", "ppppppiiiip"),
     "ts_moe_arrange": ("int", "ppppppiip"),
     "ts_moe_linear": ("int", "plpipipiipiiiffpiip"),
-    "ts_moe_combine": ("int", "pppppiiiip"),
+    "ts_moe_combine": ("int", "pppppiiiippp"),
+    "ts_moe_route_grouped": ("int", "pppppppiiiiiiffp"),
+    "ts_paged_attention_scored": ("int", "plpppllllii" "pippiiiiifiiipppl" "p"),
+    "ts_mingru_scan": ("int", "pliiiippppiplpiiiip"),
+    "ts_unary_activation_rows": ("int", "ppliffip"),
     "ts_gated_activation": ("int", "ppiiiffip"),
     "ts_sgemm_nt_batched": ("int", "pppiiilllilllp"),
-    "ts_qk_norm_rope_store": ("int", "pliiipppppfpifpppppllllii" "piiiiiiiip"),
+    "ts_qk_norm_rope_store": ("int", "pliiipppppfpifpppppllllii" "piiiiiiiiifip"),
     "ts_sigmoid_gate": ("int", "plplpliifip"),
     "ts_paged_attention_split": ("int", "plpppllllii" "pippiiiiifiip"),
     "ts_short_conv_silu": ("int", "plppppiplpiiiip"),
@@ -423,13 +427,16 @@ class Ops:
     def stream_norm(self, branch: torch.Tensor | None, w_close: torch.Tensor | None, stream: torch.Tensor,
                     w_open: torch.Tensor | None, eps: float, dtype: torch.dtype, rows: torch.Tensor | None = None,
                     table: torch.Tensor | None = None, ids: torch.Tensor | None = None, scale: float = 1.0,
-                    centered: bool = False, plain_add: bool = False) -> torch.Tensor | None:
+                    centered: bool = False, plain_add: bool = False, positions: torch.Tensor | None = None,
+                    position_frequencies: torch.Tensor | None = None) -> torch.Tensor | None:
         """
         stream (float32, in place) += closing norm of `branch` (if given; with `plain_add` the branch as
         it is); returns the opening norm of the sum in `dtype` (if `w_open` is given; with `centered` a
         layer norm without bias instead of an RMS norm).  With `rows` only those rows are normed, into a
         compact output, and the stream is left as it is.  With `table` and `ids` the rows
-        table[ids] * scale start the stream instead.  Weights are float32 and multiply as given.
+        table[ids] * scale start the stream instead, plus, with `positions` and `position_frequencies` (float32
+        [ceil(width / 2)]), the vector whose entry 2i is sin(position * frequency i) and entry 2i + 1 its cosine.
+        Weights are float32 and multiply as given.
         """
         self._check(stream, "residual stream", torch.float32, 2)
         width = stream.shape[1]
@@ -447,6 +454,11 @@ class Ops:
             self._check(ids, "token ids", torch.int32, 1)
             if table.shape[1] != width or ids.shape[0] != stream.shape[0]:
                 raise KernelError("stream_norm: the table's rows or the number of ids do not match the stream")
+        if position_frequencies is not None:
+            self._check(position_frequencies, "position frequencies", torch.float32, 1)
+            if ids is None or positions is None or position_frequencies.shape[0] < (width + 1) // 2:
+                raise KernelError("stream_norm: a position vector needs ids, positions and a frequency for every two columns")
+            self._check(positions, "positions", torch.int32, 1)
         count = stream.shape[0]
         if rows is not None:
             self._check(rows, "rows", torch.int32, 1)
@@ -456,7 +468,8 @@ class Ops:
             out = torch.empty((count, width), dtype=dtype, device=stream.device)
         self._call("ts_stream_norm", _ptr(branch), _ptr(w_close), _ptr(stream), _ptr(w_open), _ptr(out), _ptr(rows), count,
                    width, eps, _ptr(table), _ptr(ids), table.shape[0] if table is not None else 0, scale,
-                   (1 if centered else 0) | (2 if plain_add else 0), _DTYPE_CODE[dtype], _stream())
+                   (1 if centered else 0) | (2 if plain_add else 0), _DTYPE_CODE[dtype],
+                   _ptr(positions) if position_frequencies is not None else 0, _ptr(position_frequencies), _stream())
         return out
 
     # ------------------------------------------------------------------ linear recurrences
@@ -526,11 +539,14 @@ class Ops:
 
     # ------------------------------------------------------------------ attention with normed queries and keys, gated recurrences
     def qk_norm_rope_store(self, y: torch.Tensor, offsets: tuple[int, int, int], biases, weights, eps: float, position,
-                           ctx, binding, heads: int, kv_heads: int, dim: int, vdim: int) -> torch.Tensor:
+                           ctx, binding, heads: int, kv_heads: int, dim: int, vdim: int, *, norm_per_head: bool = False,
+                           q_temperature: tuple[float, int] | None = None) -> torch.Tensor:
         """
         From the projection's output y (q, k, v at the column `offsets`): biases added (float32 tensors or
-        None), q and k RMS-normed over the whole projection with `weights` (q's, k's; or None), rotated by
-        `position` (frequencies, dims, magnitude), k and v stored into the token's cache slot.  Returns q [T, heads * dim].
+        None), q and k RMS-normed over the whole projection with `weights` (q's, k's; or None; with
+        `norm_per_head` every head by itself, the weights [dim]), rotated by `position` (frequencies, dims,
+        magnitude), q multiplied by 1 + coef * ln(floor((position + 1) / every) + 1) for `q_temperature`
+        (coef, every), k and v stored into the token's cache slot.  Returns q [T, heads * dim].
         """
         if y.dtype not in _DTYPE_CODE or y.dim() != 2 or y.stride(1) != 1:
             raise KernelError("qk_norm_rope_store: y must be a [T, columns] stretch of an activation dtype")
@@ -543,25 +559,40 @@ class Ops:
             freq, rot, magnitude = position.frequencies, position.dims, float(getattr(position, "magnitude", 1.0))
         qb, kb, vb = biases if biases is not None else (None, None, None)
         qw, kw = weights if weights is not None else (None, None)
+        for w in (qw, kw):
+            if w is not None and w.numel() != (dim if norm_per_head else (heads if w is qw else kv_heads) * dim):
+                raise KernelError(f"qk_norm_rope_store: a norm weight of {w.numel()} elements")
+        coef, every = q_temperature if q_temperature is not None else (0.0, 0)
         v_page_stride, v_entry_offset = binding.value_geometry()
         self._call("ts_qk_norm_rope_store", _ptr(y), y.stride(0), offsets[0], offsets[1], offsets[2], _ptr(qb), _ptr(kb),
                    _ptr(vb), _ptr(qw), _ptr(kw), eps, _ptr(freq), rot, magnitude, _ptr(ctx.positions),
                    _ptr(ctx.seq_of_token), _ptr(q), _ptr(binding.k_pool), _ptr(binding.v_pool), binding.page_stride,
                    binding.entry_offset, v_page_stride, v_entry_offset, binding.page_tokens, binding.num_pages,
                    _ptr(binding.block_table), binding.table_width, 1 if binding.writes else 0, T, heads, kv_heads, dim,
-                   vdim, _DTYPE_CODE[y.dtype], _stream())
+                   vdim, _DTYPE_CODE[y.dtype], 1 if norm_per_head else 0, float(coef), int(every), _stream())
         return q
 
     def paged_attention_split(self, q: torch.Tensor, ctx, binding, nh: int, nkv: int, hd: int, vd: int, scale: float,
-                              window: int) -> torch.Tensor:
+                              window: int, *, weights: str = "softmax", slopes: torch.Tensor | None = None,
+                              head_bias: torch.Tensor | None = None, head_gate: torch.Tensor | None = None) -> torch.Tensor:
         """
         [T, nh * vd]: causal attention of q [T, nh * hd] over the entry's cached keys (head size hd) and
         values (head size vd).  Equal head sizes of 64 or 128 in bfloat16 run on the tensor-core kernels
         (`paged_attention`), everything else on the generic kernel.
+
+        Options: `slopes` (float32 [nh]) takes slopes[h] * (i - j) off the score of query i and key j,
+        `head_bias` (float32 [nh]) is added to every score of its head, `weights` "sigmoid" makes a visible
+        key's weight sigmoid(score) with no normalisation, `head_gate` ([T, nh] logits, a column stretch of
+        the activation dtype) multiplies head h's output by sigmoid(head_gate[t, h]).
         """
         self._check(q, "q", tuple(_DTYPE_CODE), 2)
         if q.shape[1] != nh * hd:
             raise KernelError(f"paged_attention_split: q has {q.shape[1]} columns, expected {nh * hd}")
+        if weights not in ("softmax", "sigmoid"):
+            raise KernelError(f"paged_attention_split: weights {weights!r}")
+        if weights != "softmax" or slopes is not None or head_bias is not None or head_gate is not None:
+            return self._paged_attention_scored(q, ctx, binding, nh, nkv, hd, vd, scale, window, weights, slopes, head_bias,
+                                                head_gate)
         if (hd == vd and q.dtype == torch.bfloat16 and getattr(ctx, "cu_q", None) is not None
                 and self.lib.ts_attention_bf16_supported(hd, binding.page_tokens, nh, nkv)):
             # the tensor-core kernels read q from the columns of a [q | k | v] row: q alone is such a row's first part
@@ -575,6 +606,63 @@ class Ops:
                    binding.num_pages, _ptr(binding.block_table), binding.table_width, _ptr(ctx.positions),
                    _ptr(ctx.seq_of_token), q.shape[0], nh, nkv, hd, vd, scale, window, _DTYPE_CODE[q.dtype], _stream())
         return out
+
+    def _paged_attention_scored(self, q, ctx, binding, nh, nkv, hd, vd, scale, window, weights, slopes, head_bias,
+                                head_gate) -> torch.Tensor:
+        for t, name in ((slopes, "slopes"), (head_bias, "head bias")):
+            if t is not None:
+                self._check(t, name, torch.float32, 1)
+                if t.shape[0] != nh:
+                    raise KernelError(f"paged_attention_split: {name} has {t.shape[0]} elements for {nh} heads")
+        if head_gate is not None and (head_gate.dtype != q.dtype or head_gate.dim() != 2 or head_gate.stride(1) != 1
+                                      or tuple(head_gate.shape) != (q.shape[0], nh)):
+            raise KernelError("paged_attention_split: the head gate must be a [T, heads] stretch of the activation dtype")
+        out = torch.empty((q.shape[0], nh * vd), dtype=q.dtype, device=q.device)
+        v_page_stride, v_entry_offset = binding.value_geometry()
+        self._call("ts_paged_attention_scored", _ptr(q), q.stride(0), _ptr(out), _ptr(binding.k_pool), _ptr(binding.v_pool),
+                   binding.page_stride, binding.entry_offset, v_page_stride, v_entry_offset, binding.page_tokens,
+                   binding.num_pages, _ptr(binding.block_table), binding.table_width, _ptr(ctx.positions),
+                   _ptr(ctx.seq_of_token), q.shape[0], nh, nkv, hd, vd, scale, window, _DTYPE_CODE[q.dtype],
+                   1 if weights == "sigmoid" else 0, _ptr(slopes), _ptr(head_bias), _ptr(head_gate),
+                   head_gate.stride(0) if head_gate is not None else 0, _stream())
+        return out
+
+    def mingru_scan(self, y: torch.Tensor, offsets: tuple[int, int, int], z_bias: torch.Tensor | None,
+                    x_bias: torch.Tensor | None, ctx, binding, width: int, dtype: torch.dtype) -> torch.Tensor:
+        """
+        [T, width] in `dtype`: S_t * silu(g_t) of the element-wise gated recurrence S_t = (1 - z_t) S_(t-1) + z_t c_t
+        with z = sigmoid(a + z_bias), c = u + x_bias + 1/2 where u + x_bias >= 0 and sigmoid(u + x_bias) below.
+        a, u, g are the stretches of `width` columns of y (float32 or `dtype`) at the column `offsets`; the
+        state (float32 [width]) is read from and written back to the request's slot.
+        """
+        if y.dim() != 2 or y.stride(1) != 1 or y.dtype not in (torch.float32, dtype) or dtype not in _DTYPE_CODE:
+            raise KernelError("mingru_scan: y must be a [T, columns] stretch, float32 or of the activation dtype")
+        if max(offsets) + width > y.shape[1]:
+            raise KernelError(f"mingru_scan: y has {y.shape[1]} columns, fewer than the stretches at {offsets} need")
+        for b, name in ((z_bias, "z bias"), (x_bias, "x bias")):
+            if b is not None:
+                self._check(b, name, torch.float32, 1)
+                if b.shape[0] != width:
+                    raise KernelError(f"mingru_scan: the {name} has {b.shape[0]} elements for {width} channels")
+        state, stride = self._state_floats(binding, width, "mingru_scan")
+        T = y.shape[0]
+        out = torch.empty((T, width), dtype=dtype, device=y.device)
+        self._call("ts_mingru_scan", _ptr(y), y.stride(0), offsets[0], offsets[1], offsets[2], _DTYPE_CODE[y.dtype],
+                   _ptr(z_bias), _ptr(x_bias), _ptr(ctx.cu_q), _ptr(binding.state_slots), binding.state_slots.shape[0],
+                   state.data_ptr(), stride, _ptr(out), width, T, int(getattr(ctx, "max_q_len", 0) or 0),
+                   _DTYPE_CODE[dtype], _stream())
+        return out
+
+    UNARY_ACTIVATIONS = {"relu2": 0, "xielu": 1}
+
+    def unary_activation(self, x: torch.Tensor, kind: str, a: float = 0.0, b: float = 0.0) -> torch.Tensor:
+        """act(x), in place: "relu2" relu(x)^2; "xielu" a x^2 + x/2 for x > 0 and b (exp(x) - 1 - x) + x/2 for x <= 0."""
+        self._check(x, "x", tuple(_DTYPE_CODE))
+        if kind not in self.UNARY_ACTIVATIONS:
+            raise KernelError(f"unary_activation: kind {kind!r} of {sorted(self.UNARY_ACTIVATIONS)}")
+        self._call("ts_unary_activation_rows", _ptr(x), _ptr(x), x.numel(), self.UNARY_ACTIVATIONS[kind], float(a), float(b),
+                   _DTYPE_CODE[x.dtype], _stream())
+        return x
 
     def sigmoid_gate(self, a: torch.Tensor, gate: torch.Tensor, scale: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
         """a * sigmoid(gate) * scale, [T, cols]; the operands and `out` may be column stretches of wider tensors."""
@@ -818,6 +906,38 @@ class Ops:
                    _ptr(pair_of_row), _ptr(row_of_pair), T * top, E, _stream())
         return chosen, share, offsets, pair_of_row, row_of_pair
 
+    def moe_route_grouped(self, logits: torch.Tensor, correction: torch.Tensor | None, ctx, top: int, *, real_experts: int,
+                          groups: int = 1, keep: int = 1, weight_scale: float = 1.0, share_eps: float = 0.0):
+        """
+        Routing by scores that are the softmax over ALL router outputs (logits float32 [T, outputs]): the `top`
+        outputs with the largest score + correction among the `keep` best of `groups` groups of neighbours are
+        chosen, their shares are the scores divided by their sum + share_eps, times weight_scale.  Outputs from
+        `real_experts` on are identity experts.  Returns `moe_route`'s five tensors (an identity choice has
+        chosen = -1 and no row; offsets has real_experts + 1 entries) and identity_share [T] float32 (None
+        where every output is an expert).
+        """
+        self._check(logits, "router logits", torch.float32, 2)
+        T, outputs = logits.shape
+        if correction is not None:
+            self._check(correction, "correction", torch.float32, 1)
+            if correction.shape[0] != outputs:
+                raise KernelError(f"moe_route_grouped: the correction has {correction.shape[0]} elements for {outputs} outputs")
+        dev = logits.device
+        E = real_experts
+        chosen = torch.empty((T, top), dtype=torch.int32, device=dev)
+        share = torch.empty((T, top), dtype=torch.float32, device=dev)
+        counters = torch.zeros((2 * max(E, 1),), dtype=torch.int32, device=dev)
+        offsets = torch.empty((E + 1,), dtype=torch.int32, device=dev)
+        pair_of_row = torch.zeros((T * top,), dtype=torch.int32, device=dev)
+        row_of_pair = torch.empty((T * top,), dtype=torch.int32, device=dev)
+        identity_share = torch.empty((T,), dtype=torch.float32, device=dev) if E < outputs else None
+        self._call("ts_moe_route_grouped", _ptr(logits), _ptr(correction), _ptr(getattr(ctx, "seq_of_token", None)),
+                   _ptr(chosen), _ptr(share), _ptr(counters), _ptr(identity_share), T, outputs, E, top, groups, keep,
+                   float(weight_scale), float(share_eps), _stream())
+        self._call("ts_moe_arrange", _ptr(chosen), _ptr(counters), counters.data_ptr() + 4 * max(E, 1), _ptr(offsets),
+                   _ptr(pair_of_row), _ptr(row_of_pair), T * top, E, _stream())
+        return chosen, share, offsets, pair_of_row, row_of_pair, identity_share
+
     def moe_linear(self, x: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, pair_of_row: torch.Tensor | None, top: int,
                    pairs: int, activation: str | None = None, limit: float = 0.0, alpha: float = 1.0,
                    row_scale: torch.Tensor | None = None) -> torch.Tensor:
@@ -857,14 +977,24 @@ class Ops:
         return out
 
     def moe_combine(self, y: torch.Tensor, row_of_pair: torch.Tensor, share: torch.Tensor | None,
-                    shared_out: torch.Tensor | None, num_tokens: int) -> torch.Tensor:
-        """[T, width]: sum over a token's choices of share * y[row of the pair] (share None: 1), plus the shared expert's output."""
+                    shared_out: torch.Tensor | None, num_tokens: int, x: torch.Tensor | None = None,
+                    identity_share: torch.Tensor | None = None) -> torch.Tensor:
+        """
+        [T, width]: sum over a token's choices of share * y[row of the pair] (share None: 1), plus the shared
+        expert's output, plus identity_share[t] * x[t] (the part of experts whose output is their input).
+        """
         self._check(y, "y", tuple(_DTYPE_CODE), 2)
+        if identity_share is not None:
+            self._check(identity_share, "identity share", torch.float32, 1)
+            self._check(x, "the experts' input", y.dtype, 2)
+            if tuple(x.shape) != (num_tokens, y.shape[1]) or identity_share.shape[0] != num_tokens:
+                raise KernelError("moe_combine: the experts' input and the identity shares must have a row a token")
         if shared_out is not None:
             self._check(shared_out, "shared expert output", y.dtype, 2)
         out = torch.empty((num_tokens, y.shape[1]), dtype=y.dtype, device=y.device)
         self._call("ts_moe_combine", _ptr(y), _ptr(row_of_pair), _ptr(share), _ptr(shared_out), _ptr(out), num_tokens,
-                   y.shape[1], row_of_pair.shape[0] // max(num_tokens, 1), _DTYPE_CODE[y.dtype], _stream())
+                   y.shape[1], row_of_pair.shape[0] // max(num_tokens, 1), _DTYPE_CODE[y.dtype],
+                   _ptr(x) if identity_share is not None else 0, _ptr(identity_share), _stream())
         return out
 
     def silu_mul(self, gate_up: torch.Tensor) -> torch.Tensor:

@@ -131,6 +131,8 @@ class PreNormStreamBlock(PreNormBlock):
     """
 
     takes_token_ids = True
+    takes_embedding_scale = True
+    takes_embedding_position = True
 
     @staticmethod
     def _members(spec: BlockSpec):
@@ -148,10 +150,13 @@ class PreNormStreamBlock(PreNormBlock):
         if spec.feed_forward is not None:
             self.feed_forward_norm, self.feed_forward = built[2:]
 
-    def forward(self, x, residual: torch.Tensor | None, ctx, binding, embedding: torch.Tensor | None = None):
+    def forward(self, x, residual: torch.Tensor | None, ctx, binding, embedding: torch.Tensor | None = None,
+                embedding_scale: float = 1.0, embedding_position=None):
+        """`embedding_position`: a position part whose vector is added to the scaled embedding rows."""
         from tinyserve_llm_b200.parts.norm import PendingBranch
         if embedding is not None:
-            h, residual = self.mixer_norm.forward_embedded(embedding, x)
+            h, residual = self.mixer_norm.forward_embedded(embedding, x, embedding_scale, positions=ctx.positions,
+                                                           position=embedding_position)
         else:
             h, residual = self.mixer_norm.forward(x, residual)
         branch = PendingBranch(self.mixer.forward(h, ctx, binding), None)

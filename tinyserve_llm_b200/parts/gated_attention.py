@@ -8,6 +8,13 @@ values of another head size than keys, and a sigmoid output gate on the concaten
     o_head = softmax(q . k * scale over the keys up to the query's own) v
     y = W_o (concat(o) * sigmoid(W_g h))
 
+Options a design may switch on (`GatedAttentionSpec`): a norm of q and of k head by head with one
+weight shared by the heads; a query temperature q <- q (1 + c ln(floor((p + 1) / n) + 1)) at position
+p; a distance penalty slope_h (i - j) taken off the score with slope_h = 2^(-c (h + 1) / heads); a
+number per head added to every score; sigmoid weights instead of a softmax (a visible key's weight is
+sigmoid(score), nothing is normalised over the keys); an output gate of one number a head.  With any
+of the last four the attention runs on the kernels that carry them (`paged_attention_split`'s options).
+
 Keys (rotated) and values live in the paged cache; one kernel norms, rotates and stores, one attends
 (the tensor-core kernels where keys and values share a head size they take, the generic one else),
 one gates.  The mixer can stand alone or beside others in a `ParallelMixer`, which fuses the
@@ -37,6 +44,12 @@ class GatedAttention(Mixer):
         for name, size in (("head_dim", spec.head_dim), ("value_dim", spec.value_dim)):
             if not 0 < size <= MAX_HEAD_DIM:
                 raise ValueError(f"{name}={size} is not supported: the attention kernels take up to {MAX_HEAD_DIM}")
+        if spec.qk_norm_scope not in ("projection", "head") or spec.output_gate_scope not in ("channel", "head"):
+            raise NotImplementedError(f"attention: norm scope {spec.qk_norm_scope!r}, gate scope {spec.output_gate_scope!r}")
+        if spec.weights not in ("softmax", "sigmoid"):
+            raise NotImplementedError(f"attention: weights {spec.weights!r}; have softmax and sigmoid")
+        if spec.q_temperature_every < 0 or spec.distance_slope_exponent < 0 or spec.window < 0:
+            raise ValueError("attention: q_temperature_every, distance_slope_exponent and window must not be negative")
 
     @classmethod
     def declare(cls, spec: GatedAttentionSpec) -> dict[str, TensorDecl]:
@@ -48,9 +61,13 @@ class GatedAttention(Mixer):
         if spec.bias:
             out.update({"q.b": TensorDecl((nq,)), "k.b": TensorDecl((nk,)), "v.b": TensorDecl((nv,))})
         if spec.qk_norm:
-            out.update({"q.norm": TensorDecl((nq,), init="unit"), "k.norm": TensorDecl((nk,), init="unit")})
+            per_head = spec.qk_norm_scope == "head"
+            out.update({"q.norm": TensorDecl((spec.head_dim if per_head else nq,), init="unit"),
+                        "k.norm": TensorDecl((spec.head_dim if per_head else nk,), init="unit")})
+        if spec.head_bias:
+            out["pb"] = TensorDecl((spec.num_heads,))
         if spec.output_gate:
-            out["g"] = TensorDecl((no, spec.hidden_size))
+            out["g"] = TensorDecl((spec.num_heads if spec.output_gate_scope == "head" else no, spec.hidden_size))
         return out
 
     def __init__(self, spec: GatedAttentionSpec, tensors: dict[str, torch.Tensor], rt: Runtime, fused: bool = False) -> None:
@@ -63,6 +80,13 @@ class GatedAttention(Mixer):
         self.inner_width = spec.num_heads * spec.value_dim
         self.biases = tuple(tensors[n].to(**f32).contiguous() for n in ("q.b", "k.b", "v.b")) if spec.bias else None
         self.norm_weights = tuple(tensors[n].to(**f32).contiguous() for n in ("q.norm", "k.norm")) if spec.qk_norm else None
+        self.head_bias = tensors["pb"].to(**f32).contiguous() if spec.head_bias else None
+        self.slopes = None
+        if spec.distance_slope_exponent > 0:
+            c, H = float(spec.distance_slope_exponent), spec.num_heads
+            self.slopes = torch.tensor([2.0 ** (-c * (h + 1) / H) for h in range(H)], **f32)
+        self.q_temperature = (float(spec.q_temperature_coef), int(spec.q_temperature_every)) if spec.q_temperature_every > 0 else None
+        self.gate_width = 0 if not spec.output_gate else (spec.num_heads if spec.output_gate_scope == "head" else self.inner_width)
         self.position = None
         if spec.position is not None:
             self.position = part_class("position", spec.position)(spec.position, {}, rt)
@@ -83,8 +107,20 @@ class GatedAttention(Mixer):
         s, ops = self.spec, self.rt.ops
         nq, nk, nv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim, s.num_kv_heads * s.value_dim
         q = ops.qk_norm_rope_store(y, (0, nq, nq + nk), self.biases, self.norm_weights, s.qk_norm_eps, self.position,
-                                   ctx, binding, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim)
-        o = ops.paged_attention_split(q, ctx, binding, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, s.scale, s.window)
+                                   ctx, binding, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim,
+                                   norm_per_head=s.qk_norm_scope == "head", q_temperature=self.q_temperature)
+        gate = y[:, nq + nk + nv:nq + nk + nv + self.gate_width] if s.output_gate else None
+        per_head_gate = s.output_gate and s.output_gate_scope == "head"
+        o = ops.paged_attention_split(q, ctx, binding, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, s.scale, s.window,
+                                      weights=s.weights, slopes=self.slopes, head_bias=self.head_bias,
+                                      head_gate=gate if per_head_gate else None)
+        if per_head_gate:                               # the gate went into the attention kernel's last step
+            if scale != 1.0:
+                o = o * scale
+            if out is not None:
+                out.copy_(o)
+                return out
+            return o
         if s.output_gate:
             return ops.sigmoid_gate(o, y[:, nq + nk + nv:nq + nk + nv + self.inner_width], scale, out)
         if out is not None:

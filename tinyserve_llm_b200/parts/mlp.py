@@ -9,6 +9,8 @@ Reference: model/llama.py:77-83 (silu(gate) * up), :215-225 (fused gate_up, down
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from tinyserve_llm_b200.config.spec import GatedMLPSpec, PlainMLPSpec
@@ -47,17 +49,27 @@ class GatedMLP(FeedForward):
 
 @register_part("feed_forward", "plain_mlp")
 class PlainMLP(FeedForward):
-    """Ungated feed-forward down(act(up(x))) with act the square of relu."""
+    """
+    Ungated feed-forward down(act(up(x))) with act the square of relu, or xIELU: with the two numbers
+    p, q of the layer's parameter tensor, softplus(p) z^2 + z/2 for z > 0 and
+    (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2 for z <= 0.  The two factors are worked out once, in
+    float64, when the layer is built.
+    """
 
     graph_safe = True
 
-    ACTIVATIONS = ("relu2",)
+    ACTIVATIONS = ("relu2", "xielu")
 
     @classmethod
     def declare(cls, spec: PlainMLPSpec) -> dict[str, TensorDecl]:
         up, down = spec.tensor_names
-        return {up: TensorDecl((spec.intermediate_size, spec.hidden_size)),
-                down: TensorDecl((spec.hidden_size, spec.intermediate_size))}
+        out = {up: TensorDecl((spec.intermediate_size, spec.hidden_size)),
+               down: TensorDecl((spec.hidden_size, spec.intermediate_size))}
+        if spec.activation == "xielu":
+            if not spec.param_name:
+                raise ValueError("an xIELU layer needs the name of its parameter tensor")
+            out[spec.param_name] = TensorDecl((2,))
+        return out
 
     def __init__(self, spec: PlainMLPSpec, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
         super().__init__(spec, tensors, rt)
@@ -66,7 +78,11 @@ class PlainMLP(FeedForward):
         up, down = spec.tensor_names
         self.up = Linear(tensors[up], rt)
         self.down = Linear(tensors[down], rt)
+        self.factors = (0.0, 0.0)
+        if spec.activation == "xielu":
+            p, q = (float(v) for v in tensors[spec.param_name].to(torch.float64).cpu().tolist())
+            softplus = lambda v: v if v > 30 else math.log1p(math.exp(v))  # noqa: E731
+            self.factors = (softplus(p), 0.5 + softplus(q))
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        h = self.up(x)
-        return self.down(torch.relu(h).square_())
+        return self.down(self.rt.ops.unary_activation(self.up(x), self.spec.activation, *self.factors))

@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from tinyserve_llm_b200.config.spec import ModelSpec
-from tinyserve_llm_b200.parts import (attention, delta_rule, gated_attention, latent_attention, mlp, mlstm,  # noqa: F401  (registration)
+from tinyserve_llm_b200.parts import (attention, delta_rule, gated_attention, latent_attention, mingru, mlp, mlstm,  # noqa: F401  (registration)
                                       norm, parallel, recurrence, rotary, routed_experts)
 from tinyserve_llm_b200.parts.base import KVNeed, Runtime, TensorDecl, arrangement_class, part_class
 from tinyserve_llm_b200.parts.block import _sub
@@ -49,6 +49,9 @@ class DecoderModel:
             self.lm_head.out_features, self.lm_head.in_features = self.embedding.shape
         else:
             self.lm_head = Linear(tensors[spec.lm_head_name], rt)
+        self.embedding_position = None
+        if spec.embedding_position is not None:
+            self.embedding_position = part_class("position", spec.embedding_position)(spec.embedding_position, {}, rt)
         self._check_run_list()
         # A CUDA graph may replay the model only if no part runs host code that depends on the step.
         self.graph_safe = all(getattr(part, "graph_safe", False) for block in self.blocks
@@ -89,9 +92,13 @@ class DecoderModel:
         run = self.spec.run
         first = self.blocks[run[0].block] if run else None
         scale = float(self.spec.embedding_scale)
+        if self.embedding_position is not None and not getattr(first, "takes_embedding_position", False):
+            raise NotImplementedError("a position vector on the embedding needs a first block whose arrangement takes it")
         if first is not None and getattr(first, "takes_token_ids", False) and (
                 scale == 1.0 or getattr(first, "takes_embedding_scale", False)):
             extra = {"embedding_scale": scale} if scale != 1.0 else {}
+            if self.embedding_position is not None:
+                extra["embedding_position"] = self.embedding_position
             x, residual = first.forward(ctx.token_ids, None, ctx, ctx.binding(run[0]), embedding=self.embedding, **extra)
             run = run[1:]
         elif scale != 1.0:

@@ -93,10 +93,13 @@ class StreamRMSNorm(Norm):
         """stream += closing(branch), with no norm of the sum."""
         self.rt.ops.stream_norm(branch, self.weight, residual, None, self.eps, self.rt.dtype)
 
-    def forward_embedded(self, table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0):
+    def forward_embedded(self, table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0, positions: torch.Tensor | None = None,
+                         position=None):
+        """`position` (a part with `frequencies`) and `positions`: its vector is added to the scaled rows."""
         residual = torch.empty((ids.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
         out = self.rt.ops.stream_norm(None, None, residual, self.weight, self.eps, self.rt.dtype, table=table, ids=ids,
-                                      scale=scale, centered=self.centered)
+                                      scale=scale, centered=self.centered, positions=positions,
+                                      position_frequencies=position.frequencies if position is not None else None)
         return out, residual
 
 

@@ -13,7 +13,7 @@ import math
 
 import torch
 
-from tinyserve_llm_b200.config.spec import Llama3Scaling, RotarySpec
+from tinyserve_llm_b200.config.spec import Llama3Scaling, RotarySpec, SinusoidSpec
 from tinyserve_llm_b200.parts.base import PositionEncoding, Runtime, register_part
 
 
@@ -87,3 +87,23 @@ class InlineRotary(PositionEncoding):
         self.frequencies = rt.shared[key]
         # cos and sin are multiplied by this (1 without YaRN); a kernel that rotates with a YaRN rescaling has to apply it
         self.magnitude = 1.0 if spec.yarn is None else 0.1 * math.log(spec.yarn.factor) + 1.0
+
+
+@register_part("position", "sinusoid")
+class Sinusoid(PositionEncoding):
+    """
+    A position vector added to the token embedding: with angle_i = position * base^(-2i/size), entry 2i is
+    sin(angle_i) and entry 2i + 1 cos(angle_i).  Only the frequencies are kept (worked out in float64, stored
+    in float32); the kernel that gathers the embedding rows multiplies them by the position in float32 and
+    takes sine and cosine itself, so there is no table and no longest position.
+    """
+
+    def __init__(self, spec: SinusoidSpec, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
+        super().__init__(spec, tensors, rt)
+        if spec.size <= 0 or spec.base <= 0:
+            raise ValueError(f"a sinusoidal position vector of {spec.size} entries with base {spec.base}")
+        key = ("sinusoid", spec)
+        if key not in rt.shared:
+            i = torch.arange((spec.size + 1) // 2, dtype=torch.float64)
+            rt.shared[key] = (float(spec.base) ** (-2.0 * i / spec.size)).to(torch.float32).to(rt.device)
+        self.frequencies = rt.shared[key]
