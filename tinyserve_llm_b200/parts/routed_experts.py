@@ -36,9 +36,9 @@ class RoutedExperts(FeedForward):
 
     @classmethod
     def declare(cls, spec: RoutedExpertsSpec) -> dict[str, TensorDecl]:
-        if spec.expert is None or not 0 < spec.top <= spec.num_experts:
+        if spec.expert is None or not 0 < spec.top <= spec.num_experts + spec.identity_experts:
             raise ValueError(f"routed experts need an expert description and 0 < top <= experts, got top={spec.top}, "
-                             f"experts={spec.num_experts}")
+                             f"experts={spec.num_experts + spec.identity_experts}")
         if spec.scoring not in ("softmax_chosen", "sigmoid", "softmax_all") or spec.weight_on not in ("output", "input"):
             raise NotImplementedError(f"routed experts: scoring {spec.scoring!r}, weight on {spec.weight_on!r}")
         outputs = spec.num_experts + spec.identity_experts
