@@ -297,6 +297,72 @@ def test_a_key_at_a_page_border_is_seen_to_the_windows_edge_and_no_further(dtype
     torch.testing.assert_close(portion, want, **TOL[dtype])
 
 
+@pytest.mark.parametrize("heads, kv_heads, dim, window", [(4, 2, 64, 100), (6, 1, 128, 257), (2, 2, 64, 1000), (16, 2, 128, 64)])
+def test_sigmoid_attention_at_the_tensor_core_kernels_sizes(heads, kv_heads, dim, window):
+    """
+    Keys and values of 64 and of 128 channels a head on pages of 64 tokens in bfloat16: a prompt's portions run in
+    tiles of 64 queries against tiles of 64 keys, single tokens in splits of 256 keys that are merged.  Two
+    requests of unequal length, in portions that end inside tiles, with windows that begin inside a tile, at
+    its edge and before the first key, then token by token across a split's edge; a portion beside single
+    tokens in one step.
+    """
+    dtype, width = torch.bfloat16, 64
+    spec, m = _attention_spec(width, heads, kv_heads, dim, dim, 0.2, window, 0.3, 50)
+
+    def edit(t):
+        t["pb"] = torch.linspace(-3.0, -1.0, heads).to(t["pb"].dtype)
+
+    mixer, w = _mixer(spec, dtype, 7, edit)
+    g = torch.Generator().manual_seed(3)
+    lens = [530, 203]
+    x_of = [torch.randn(n, width, generator=g).to(dtype) for n in lens]
+    want = [plain.sigmoid_attention(x.double(), w, m, 1e-5) for x in x_of]
+    cuts = [[(0, 130), (0, 2)], [(130, 131), (2, 67)], [(131, 390), (67, 68)], [(390, 507), (68, 190)]]
+    cuts += [[(i, i + 1), (min(190 + i - 507, 203), min(191 + i - 507, 203))] for i in range(507, 530)]
+    got = _in_steps(_Slots(mixer, dtype, lens, page=64), x_of, cuts)
+    for a, b in zip(got, want):
+        rows_close(a, b, dtype)
+
+
+def test_a_far_key_stands_out_through_the_tensor_core_kernels():
+    """
+    As the test at a page's border, at head sizes the tensor-core kernels take: one key at the last slot of a
+    page of 64 tokens weighs nearly 1, every other next to nothing; queries see it up to window - 1 positions
+    later and no further, in a portion whose tile holds the edge and as single tokens whose split holds it.
+    """
+    dtype, width, heads, dim, far, window = torch.bfloat16, 32, 2, 64, 127, 300
+    spec, m = _attention_spec(width, heads, 1, dim, dim, 1.0, window, 0.0, 1)
+
+    def edit(t):
+        t["q"] = torch.zeros_like(t["q"])
+        t["q"][0, 0] = t["q"][dim, 0] = 1.0
+        t["k"] = t["k"] * 0.5
+        t["k"][0] = 0.0
+        t["k"][0, 1] = 1.0
+        t["k"][:, :2] = t["k"][:, :2] * (torch.arange(dim)[:, None] == 0)
+        t["q.norm"] = torch.ones_like(t["q.norm"])
+        t["k.norm"] = torch.ones_like(t["k.norm"])
+        t["pb"] = torch.full_like(t["pb"], -12.0)
+        t["g"] = torch.zeros_like(t["g"])
+
+    mixer, w = _mixer(spec, dtype, 5, edit)
+    g = torch.Generator().manual_seed(2)
+    n = far + window + 40
+    x = torch.randn(n, width, generator=g) * 0.3
+    x[:, 0] = 6.0
+    x[:, 1] = 0.0
+    x[far, 1] = 40.0
+    x = x.to(dtype)
+    want = plain.sigmoid_attention(x.double(), w, m, 1e-5)
+    edge = far + window
+    assert float((want[edge - 1] - want[edge]).norm()) > 10 * float((want[edge] - want[edge + 1]).norm())     # the premise
+    single = _in_steps(_Slots(mixer, dtype, [n], page=64), [x],
+                       [[(0, 64)], [(64, edge - 3)], *[[(i, i + 1)] for i in range(edge - 3, edge + 4)], [(edge + 4, n)]])[0]
+    torch.testing.assert_close(single, want, **TOL[dtype])
+    portion = _in_steps(_Slots(mixer, dtype, [n], page=64), [x], [[(0, far + 1)], [(far + 1, edge - 7)], [(edge - 7, edge + 9)], [(edge + 9, n)]])[0]
+    torch.testing.assert_close(portion, want, **TOL[dtype])
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_query_temperature_steps_at_its_positions(dtype):
     """ops.qk_norm_rope_store alone: every head normed by itself, q scaled by 1 + c ln(floor((p + 1) / n) + 1) from position 0 on."""

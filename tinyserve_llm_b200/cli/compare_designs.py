@@ -1,9 +1,9 @@
 """
 Prefill and decode throughput of a design at layer sizes that resemble a real model's, beside the
 engine's closest other design at equal width and depth (Duduvik beside Llama, Nipizen beside
-Duduvik), both with random weights through the engine's own step function:
+Duduvik, Lugipel beside Nipizen), both with random weights through the engine's own step function:
 
-    python bench.py --design duduvik|nipizen [--size small|medium|large] [--steps K] [--warmup W]
+    python bench.py --design duduvik|nipizen|lugipel [--size small|medium|large] [--steps K] [--warmup W]
 
 For each design: a prompt of `prefill` tokens in one step (launched kernel by kernel), and decode
 steps of `batch` requests at `context` tokens each (replayed from a CUDA graph), timed on the device
@@ -68,6 +68,27 @@ def nipizen_config(s: dict) -> dict:
     mixers = (par, mem, par)
     return {"architecture": "Nipizen", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-6},
             "layers": [dict(mixers[i % 3], mlp=moe) for i in range(s["layers"])]}
+
+
+def lugipel_config(s: dict) -> dict:
+    """
+    Layers in the order attention / minGRU / attention; routed experts (top 4 of `experts` and two identity
+    experts, the best two of four groups) behind the attention layers, a dense xIELU layer behind the recurrent
+    ones.  Attention heads of 128 channels for keys and values, 4 query heads a key/value head, a window of
+    1,024 tokens; the recurrence is twice as wide as the stream.
+    """
+    width, heads = s["width"], s["heads"]
+    dim = width // heads                                   # 128 at every size
+    att = {"type": "attention",
+           "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                     "mask": {"size": 1024}, "q_temp": {"coef": 0.1, "every": 128}}}
+    gru = {"type": "mingru", "mixer": {"width": 2 * width}}
+    moe = {"kind": "moe", "expert": {"ff": s["expert_ff"]},
+           "router": {"experts": s["experts"] - 2, "identity": 2, "top": 4, "scale": 2.0, "groups": {"count": 4, "keep": 2}}}
+    dense = {"kind": "dense", "ff": s["ff"]}
+    layers = [dict(gru, mlp=dense) if i % 3 == 1 else dict(att, mlp=moe) for i in range(s["layers"])]
+    return {"architecture": "Lugipel", "vocab": VOCAB, "width": width, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-6},
+            "layers": layers}
 
 
 def llama_config(s: dict) -> dict:
@@ -199,8 +220,10 @@ def run(design: str, size: str, steps: int, warmup: int, peaks: dict) -> int:
         pair = (("llama", llama_config(s), False), ("duduvik", duduvik_config(s), True))
     elif design == "nipizen":
         pair = (("duduvik", duduvik_config(s), True), ("nipizen", nipizen_config(s), True))
+    elif design == "lugipel":
+        pair = (("nipizen", nipizen_config(s), True), ("lugipel", lugipel_config(s), True))
     else:
-        raise SystemExit(f"--design {design!r}: have ['duduvik', 'nipizen']")
+        raise SystemExit(f"--design {design!r}: have ['duduvik', 'nipizen', 'lugipel']")
     for name, cfg, profile in pair:
         record = {"design": name, "size": size, "width": s["width"], "layers": s["layers"], "dtype": "bf16",
                   "data": "synthetic", "timing": "CUDA events, median, L2 flushed between timed steps", "peaks": peaks}

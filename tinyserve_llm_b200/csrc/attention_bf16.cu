@@ -21,6 +21,7 @@
 #include "attention_bf16.h"
 
 #include "common.cuh"
+#include "mma_tile.cuh"
 
 namespace {
 
@@ -31,59 +32,18 @@ constexpr int SPLIT = DW * DKT;     // keys per decode split
 static_assert(DKT % 16 == 0 && TILE % DKT == 0, "a decode tile is a multiple of 16 keys and divides a prefill tile (and so a page)");
 constexpr float LOG2E = 1.4426950408889634f;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
-    const int bytes = valid ? 16 : 0;                       // 0: the 16 bytes are zero-filled
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(bytes));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
-}
-__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
 // 2^x for x <= 0 (and -inf): one instruction; results below the normal range flush to zero.
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
+// 2^x for any x: above the float range the result is +inf, below it 0.
+__device__ __forceinline__ float fast_exp2_any(float x) {
+    float y;
+    asm("ex2.approx.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
 }
-
-// A tile in shared memory: ROWS rows of HD bfloat16, 16-byte chunks XOR-swizzled by the row.
-template <int HD>
-__device__ __forceinline__ __nv_bfloat16* tile_at(__nv_bfloat16* tile, int row, int chunk) {
-    return tile + row * HD + ((chunk ^ (row & 7)) << 3);
-}
-
-// Loads `rows` rows of HD bfloat16 (row r from src + r * src_stride) into a swizzled tile with the
-// `nthreads` threads given; rows >= valid_rows are zero-filled.
-template <int HD>
-__device__ __forceinline__ void load_tile(__nv_bfloat16* tile, const __nv_bfloat16* src, long long src_stride,
-                                          int rows, int valid_rows, int tid, int nthreads) {
-    constexpr int CHUNKS = HD / 8;
-    for (int i = tid; i < rows * CHUNKS; i += nthreads) {
-        const int r = i / CHUNKS, c = i % CHUNKS;
-        const bool ok = r < valid_rows;
-        cp_async16(tile_at<HD>(tile, r, c), src + (ok ? (long long)r * src_stride + c * 8 : 0), ok);
-    }
-}
-
 // One warp loads a tile whose ROWS rows lie back to back in memory (a head's keys of one page).
 // Lane l takes 16-byte chunk l % CHUNKS of rows l / CHUNKS + j * (32 / CHUNKS): the row is
 // r0 | const_j, so its swizzle is (chunk ^ r0) ^ const_j and every address is one base plus constants.
@@ -123,10 +83,15 @@ struct RowState {
 // FIRST: the state is fresh (no key seen yet), so there is nothing to rescale.  TOP: only rows 0..7 of
 // the tile are real (a decode group of at most 8 heads); the softmax of rows 8..15 is skipped, their
 // probabilities are zero.
-template <int HD, bool MASK, int KT = TILE, bool FIRST = false, bool TOP = false>
+// SIG: a visible key's weight is sigmoid(score * scale - slope (pos - key) + bias) and nothing is normalised
+// over the keys: no maximum, no sum, no rescaling; slope2 and bias2 are the rows' slope and bias times log2(e).
+// The rows' maxima are set to 0, so that the merges of warps and splits, which weigh a share by
+// exp2(its maximum - the largest), add the shares as they are.
+template <int HD, bool MASK, int KT = TILE, bool FIRST = false, bool TOP = false, bool SIG = false>
 __device__ __forceinline__ void attend_tile(RowState<HD>& st, const uint32_t (&q)[HD / 16][4], __nv_bfloat16* k_tile,
                                             __nv_bfloat16* v_tile, int key0, const int (&pos)[2], const int (&lo)[2],
-                                            float scale_log2, int lane) {
+                                            float scale_log2, int lane, const float (&slope2)[2] = {0.f, 0.f},
+                                            const float (&bias2)[2] = {0.f, 0.f}) {
     float s[KT / 8][4];
 #pragma unroll
     for (int n = 0; n < KT / 8; ++n)
@@ -145,6 +110,25 @@ __device__ __forceinline__ void attend_tile(RowState<HD>& st, const uint32_t (&q
             mma_bf16(s[2 * nb + 1], q[kk], b[2], b[3]);
         }
     }
+    uint32_t p[KT / 16][4];
+    if (SIG) {
+#pragma unroll
+        for (int n = 0; n < KT / 8; ++n) {
+            float w[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int e = 0; e < (TOP ? 2 : 4); ++e) {
+                const int r = e >> 1;
+                const int key = key0 + n * 8 + ((lane & 3) << 1) + (e & 1);
+                // -(score in powers of two); exp2 of a large value is +inf and the weight 0
+                const float t = -fmaf(s[n][e], scale_log2, fmaf(slope2[r], (float)(key - pos[r]), bias2[r]));
+                w[e] = __fdividef(1.f, 1.f + fast_exp2_any(t));
+                if (MASK && !(key <= pos[r] && key >= lo[r])) w[e] = 0.f;
+            }
+            p[n >> 1][(n & 1) * 2 + 0] = pack_bf16(w[0], w[1]);
+            p[n >> 1][(n & 1) * 2 + 1] = pack_bf16(w[2], w[3]);
+        }
+        st.m[0] = st.m[1] = 0.f;
+    } else {
     // mask, running maximum (of raw scores; the scale is positive and joins the exponent below)
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -178,7 +162,6 @@ __device__ __forceinline__ void attend_tile(RowState<HD>& st, const uint32_t (&q
         }
     }
     // P = exp2(S - m), sums in float32, P rounded to bfloat16 for the second product
-    uint32_t p[KT / 16][4];
 #pragma unroll
     for (int n = 0; n < KT / 8; ++n) {
         const float p0 = fast_exp2(fmaf(s[n][0], scale_log2, -m_use[0])), p1 = fast_exp2(fmaf(s[n][1], scale_log2, -m_use[0]));
@@ -191,6 +174,7 @@ __device__ __forceinline__ void attend_tile(RowState<HD>& st, const uint32_t (&q
         st.l[1] += p2 + p3;
         p[n >> 1][(n & 1) * 2 + 0] = pack_bf16(p0, p1);
         p[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
     }
     // O += P V
 #pragma unroll
@@ -208,7 +192,8 @@ __device__ __forceinline__ void attend_tile(RowState<HD>& st, const uint32_t (&q
 }
 
 struct AttnParams {
-    const __nv_bfloat16* qkv;
+    const __nv_bfloat16* qkv;  // queries: row t at t * q_stride, head h at h * HD
+    long long q_stride;
     __nv_bfloat16* out;
     const __nv_bfloat16* k_pool;
     const __nv_bfloat16* v_pool;
@@ -225,24 +210,19 @@ struct AttnParams {
     float* partial_o;      // [seq][head][split][HD]
     float* partial_ml;     // [seq][head][split][2]
     int max_splits;
+    // sigmoid weights (the SIG kernels): terms of the score and the output gate; a null pointer: the term is absent
+    const float* slopes;          // [nh]: slopes[h] * (position - key) is taken off the score
+    const float* head_bias;       // [nh]: added to every score of the head
+    const __nv_bfloat16* gate;    // [tokens, nh] logits, gate_stride elements a row: the head's output times their sigmoid
+    long long gate_stride;
 };
 
-// Address of key (or value) row `key` of kv head `kvh` of the request whose table is given; null if
-// the page was given back.
-template <int HD>
-__device__ __forceinline__ const __nv_bfloat16* kv_row_of_page(const __nv_bfloat16* pool, const KVGeometry& geo, int page,
-                                                               int kvh, int key) {
-    if (page < 0 || page >= geo.num_pages) return nullptr;
-    return pool + (long long)page * geo.page_stride + geo.entry_offset + ((long long)kvh * geo.page_tokens + key % geo.page_tokens) * HD;
-}
-template <int HD>
-__device__ __forceinline__ const __nv_bfloat16* kv_row(const __nv_bfloat16* pool, const KVGeometry& geo,
-                                                       const int* table, int kvh, int key) {
-    return kv_row_of_page<HD>(pool, geo, table[key / geo.page_tokens], kvh, key);
+__device__ __forceinline__ float head_gate(const AttnParams& p, long long token, int head) {
+    return p.gate ? 1.f / (1.f + __expf(-__bfloat162float(p.gate[token * p.gate_stride + head]))) : 1.f;
 }
 
 // ------------------------------------------------------------------------------------------------ prefill
-template <int HD>
+template <int HD, bool SIG>
 __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);             // [64][HD]
@@ -260,7 +240,7 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
     const int pos0 = ctx - q_len + row0;                                              // position of that query
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = head / (p.nh / p.nkv);
-    const int row_width = (p.nh + 2 * p.nkv) * HD;
+    const long long row_width = p.q_stride;
     const int* table = p.block_table + (long long)seq * p.table_width;
 
     load_tile<HD>(q_tile, p.qkv + (long long)(q_begin + row0) * row_width + (long long)head * HD, row_width, TILE, rows,
@@ -300,6 +280,11 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
         lo[r] = p.window > 0 ? max(0, pos[r] - p.window + 1) : 0;
     }
     RowState<HD> st;
+    float slope2[2] = {0.f, 0.f}, bias2[2] = {0.f, 0.f};
+    if (SIG) {
+        slope2[0] = slope2[1] = p.slopes ? p.slopes[head] * LOG2E : 0.f;
+        bias2[0] = bias2[1] = p.head_bias ? p.head_bias[head] * LOG2E : 0.f;
+    }
     // positions of the warp's first and last real row: tiles wholly visible to all 16 rows need no mask
     const int warp_rows = min(rows - warp * 16, 16);
     const int warp_first = pos0 + warp * 16, warp_last = warp_first + warp_rows - 1;
@@ -313,9 +298,11 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
         const int key0 = kt * TILE;
         if (warp_rows > 0 && key0 <= warp_last) {           // else: all of the warp's rows lie before this tile
             if (warp_rows == 16 && key0 + TILE - 1 <= warp_first && key0 >= warp_lo_last)
-                attend_tile<HD, false>(st, q, k_tile, k_tile + TILE * HD, key0, pos, lo, p.scale_log2, lane);
+                attend_tile<HD, false, TILE, false, false, SIG>(st, q, k_tile, k_tile + TILE * HD, key0, pos, lo, p.scale_log2,
+                                                                lane, slope2, bias2);
             else
-                attend_tile<HD, true>(st, q, k_tile, k_tile + TILE * HD, key0, pos, lo, p.scale_log2, lane);
+                attend_tile<HD, true, TILE, false, false, SIG>(st, q, k_tile, k_tile + TILE * HD, key0, pos, lo, p.scale_log2,
+                                                               lane, slope2, bias2);
         }
     }
     // rows' sums over the quad, then write
@@ -328,7 +315,7 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
     for (int r = 0; r < 2; ++r) {
         const int tile_row = warp * 16 + (lane >> 2) + r * 8;
         if (tile_row >= rows) continue;
-        const float inv = st.l[r] > 0.f ? 1.f / st.l[r] : 0.f;
+        const float inv = SIG ? head_gate(p, q_begin + row0 + tile_row, head) : (st.l[r] > 0.f ? 1.f / st.l[r] : 0.f);
         __nv_bfloat16* o = p.out + ((long long)(q_begin + row0 + tile_row) * p.nh + head) * HD + ((lane & 3) << 1);
 #pragma unroll
         for (int n = 0; n < HD / 8; ++n)
@@ -338,7 +325,7 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
 }
 
 // ------------------------------------------------------------------------------------------------ decode
-template <int HD>
+template <int HD, bool SIG>
 __global__ void __launch_bounds__(DW * 32) decode_attention_kernel(AttnParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
@@ -374,7 +361,7 @@ __global__ void __launch_bounds__(DW * 32) decode_attention_kernel(AttnParams p)
     __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __nv_bfloat16* k_tile = q_tile + 16 * HD + warp * 2 * DKT * HD;
     __nv_bfloat16* v_tile = k_tile + DKT * HD;
-    const int row_width = (p.nh + 2 * p.nkv) * HD;
+    const long long row_width = p.q_stride;
     const bool warp_active = key0 <= pos && key0 + DKT > first_key;
     const bool holds_new = warp_active && key0 + DKT > pos;
     const __nv_bfloat16 *k_src = nullptr, *v_src = nullptr;
@@ -416,12 +403,23 @@ __global__ void __launch_bounds__(DW * 32) decode_attention_kernel(AttnParams p)
         const int posv[2] = {pos, pos};
         const int lov[2] = {first_key, first_key};
         const bool masked = holds_new || key0 < first_key;     // else every key of the tile is visible
+        float slope2[2] = {0.f, 0.f}, bias2[2] = {0.f, 0.f};
+        if (SIG) {
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {                      // the thread's rows are heads of the group
+                const int row = (lane >> 2) + r * 8;
+                if (row < g) {
+                    slope2[r] = p.slopes ? p.slopes[kvh * g + row] * LOG2E : 0.f;
+                    bias2[r] = p.head_bias ? p.head_bias[kvh * g + row] * LOG2E : 0.f;
+                }
+            }
+        }
         if (g <= 8) {
-            if (masked) attend_tile<HD, true, DKT, true, true>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane);
-            else attend_tile<HD, false, DKT, true, true>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane);
+            if (masked) attend_tile<HD, true, DKT, true, true, SIG>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane, slope2, bias2);
+            else attend_tile<HD, false, DKT, true, true, SIG>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane, slope2, bias2);
         } else {
-            if (masked) attend_tile<HD, true, DKT, true, false>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane);
-            else attend_tile<HD, false, DKT, true, false>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane);
+            if (masked) attend_tile<HD, true, DKT, true, false, SIG>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane, slope2, bias2);
+            else attend_tile<HD, false, DKT, true, false, SIG>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane, slope2, bias2);
         }
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -481,7 +479,9 @@ __global__ void __launch_bounds__(DW * 32) decode_attention_kernel(AttnParams p)
 // has them whenever the step's longest request needs them): how a request's splits are merged depends on
 // its own length only, never on what else is in the step.
 constexpr int COMBINE_CHUNK = 16;
-template <int HD, int GROUPS>
+// SIG: the splits' maxima are 0 (empty ones -inf), so the shares are added as they are; nothing divides by a sum
+// and the head's gate is the last factor.
+template <int HD, int GROUPS, bool SIG>
 __global__ void __launch_bounds__(GROUPS * HD) decode_combine_kernel(AttnParams p) {
     __shared__ float group_o[GROUPS][HD];
     __shared__ float2 group_ml[GROUPS];
@@ -544,14 +544,15 @@ __global__ void __launch_bounds__(GROUPS * HD) decode_combine_kernel(AttnParams 
         l += group_ml[g].y * f;
         o += group_o[g][d] * f;
     }
-    p.out[((long long)q_begin * p.nh + head) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+    p.out[((long long)q_begin * p.nh + head) * HD + d] =
+        __float2bfloat16_rn(SIG ? o * head_gate(p, q_begin, head) : (l > 0.f ? o / l : 0.f));
 }
 
-template <int HD>
+template <int HD, bool SIG>
 int launch(const AttnParams& p, int max_q_len, int min_q_len, int max_ctx_len, int num_prefill_seqs, cudaStream_t stream) {
     if (max_q_len > 1) {
         const size_t smem = (size_t)(TILE * HD + 4 * TILE * HD) * sizeof(__nv_bfloat16);
-        auto kernel = prefill_attention_kernel<HD>;
+        auto kernel = prefill_attention_kernel<HD, SIG>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         dim3 grid((max_q_len + TILE - 1) / TILE, p.nh, p.prefill_seqs ? num_prefill_seqs : p.num_seqs);
         kernel<<<grid, 128, smem, stream>>>(p);
@@ -561,17 +562,17 @@ int launch(const AttnParams& p, int max_q_len, int min_q_len, int max_ctx_len, i
         const size_t tiles = (size_t)(16 + DW * 2 * DKT) * HD * sizeof(__nv_bfloat16);
         const size_t merge = (size_t)(DW * 16 * (HD + 8) + DW * 16 * 2) * sizeof(float);
         const size_t smem = tiles > merge ? tiles : merge;
-        auto kernel = decode_attention_kernel<HD>;
+        auto kernel = decode_attention_kernel<HD, SIG>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         const int splits = (max_ctx_len + SPLIT - 1) / SPLIT;
         if (splits > p.max_splits) return ts_fail("decode_attention: %d splits needed, scratch holds %d", splits, p.max_splits);
         dim3 grid(splits, p.nkv, p.num_seqs);
         TS_CHAINED_CHECK("decode_attention", launch_chained(kernel, grid, dim3(DW * 32), smem, stream, p));
         if (splits <= COMBINE_CHUNK)
-            TS_CHAINED_CHECK("decode_combine", launch_chained(decode_combine_kernel<HD, 1>, dim3(p.nh, p.num_seqs), dim3(HD), 0,
+            TS_CHAINED_CHECK("decode_combine", launch_chained(decode_combine_kernel<HD, 1, SIG>, dim3(p.nh, p.num_seqs), dim3(HD), 0,
                                                               stream, p));
         else
-            TS_CHAINED_CHECK("decode_combine", launch_chained(decode_combine_kernel<HD, 256 / HD>, dim3(p.nh, p.num_seqs),
+            TS_CHAINED_CHECK("decode_combine", launch_chained(decode_combine_kernel<HD, 256 / HD, SIG>, dim3(p.nh, p.num_seqs),
                                                               dim3(256), 0, stream, p));
     }
     return 0;
@@ -589,14 +590,16 @@ TS_API int ts_attention_bf16_supported(int hd, int page_tokens, int nh, int nkv)
     return (hd == 64 || hd == 128) && page_tokens % TILE == 0 && nkv > 0 && nh % nkv == 0 && nh / nkv <= 16;
 }
 
-// The arguments are described in attention_bf16.h.  (A prefill CTA that only finds out it has nothing
-// to do still holds its shared memory while it does: hence prefill_seqs.)
-TS_API int ts_paged_attention_bf16(const void* qkv, void* out, const void* k_pool, const void* v_pool,
-                                   long long page_stride, long long entry_offset, int page_tokens, int num_pages,
-                                   const int* block_table, int table_width, const int* cu_q, const int* ctx_lens,
-                                   int num_seqs, int max_q_len, int min_q_len, int max_ctx_len, int nh, int nkv, int hd,
-                                   float scale, int window, float* scratch, long long scratch_floats,
-                                   const int* prefill_seqs, int num_prefill_seqs, cudaStream_t stream) {
+namespace {
+
+// (A prefill CTA that only finds out it has nothing to do still holds its shared memory while it does: hence
+// prefill_seqs.)
+int run(const void* q, long long q_stride, void* out, const void* k_pool, const void* v_pool, long long page_stride,
+        long long entry_offset, int page_tokens, int num_pages, const int* block_table, int table_width, const int* cu_q,
+        const int* ctx_lens, int num_seqs, int max_q_len, int min_q_len, int max_ctx_len, int nh, int nkv, int hd,
+        float scale, int window, float* scratch, long long scratch_floats, const int* prefill_seqs, int num_prefill_seqs,
+        bool sigmoid, const float* slopes, const float* head_bias, const void* gate, long long gate_stride,
+        cudaStream_t stream) {
     TS_REQUIRE(ts_attention_bf16_supported(hd, page_tokens, nh, nkv),
                "paged_attention_bf16: head_dim %d / page %d / heads %d:%d is not taken by the tensor-core kernels", hd,
                page_tokens, nh, nkv);
@@ -604,7 +607,12 @@ TS_API int ts_paged_attention_bf16(const void* qkv, void* out, const void* k_poo
     TS_REQUIRE(num_seqs <= 65535 && nh <= 65535, "paged_attention_bf16: more than 65535 requests or heads in a step");
     if (num_seqs == 0 || max_q_len <= 0) return 0;
     AttnParams p;
-    p.qkv = (const __nv_bfloat16*)qkv;
+    p.qkv = (const __nv_bfloat16*)q;
+    p.q_stride = q_stride;
+    p.slopes = slopes;
+    p.head_bias = head_bias;
+    p.gate = (const __nv_bfloat16*)gate;
+    p.gate_stride = gate_stride;
     p.out = (__nv_bfloat16*)out;
     p.k_pool = (const __nv_bfloat16*)k_pool;
     p.v_pool = (const __nv_bfloat16*)v_pool;
@@ -631,6 +639,38 @@ TS_API int ts_paged_attention_bf16(const void* qkv, void* out, const void* k_poo
         TS_REQUIRE((long long)table_width * page_tokens >= max_ctx_len,
                    "paged_attention_bf16: block tables of %d pages do not reach %d tokens", table_width, max_ctx_len);
     }
-    if (hd == 64) return launch<64>(p, max_q_len, min_q_len, max_ctx_len, num_prefill_seqs, stream);
-    return launch<128>(p, max_q_len, min_q_len, max_ctx_len, num_prefill_seqs, stream);
+    if (sigmoid) {
+        if (hd == 64) return launch<64, true>(p, max_q_len, min_q_len, max_ctx_len, num_prefill_seqs, stream);
+        return launch<128, true>(p, max_q_len, min_q_len, max_ctx_len, num_prefill_seqs, stream);
+    }
+    if (hd == 64) return launch<64, false>(p, max_q_len, min_q_len, max_ctx_len, num_prefill_seqs, stream);
+    return launch<128, false>(p, max_q_len, min_q_len, max_ctx_len, num_prefill_seqs, stream);
+}
+
+}  // namespace
+
+// The arguments are described in attention_bf16.h.
+TS_API int ts_paged_attention_bf16(const void* qkv, void* out, const void* k_pool, const void* v_pool,
+                                   long long page_stride, long long entry_offset, int page_tokens, int num_pages,
+                                   const int* block_table, int table_width, const int* cu_q, const int* ctx_lens,
+                                   int num_seqs, int max_q_len, int min_q_len, int max_ctx_len, int nh, int nkv, int hd,
+                                   float scale, int window, float* scratch, long long scratch_floats,
+                                   const int* prefill_seqs, int num_prefill_seqs, cudaStream_t stream) {
+    return run(qkv, (long long)(nh + 2 * nkv) * hd, out, k_pool, v_pool, page_stride, entry_offset, page_tokens, num_pages,
+               block_table, table_width, cu_q, ctx_lens, num_seqs, max_q_len, min_q_len, max_ctx_len, nh, nkv, hd, scale,
+               window, scratch, scratch_floats, prefill_seqs, num_prefill_seqs, false, nullptr, nullptr, nullptr, 0, stream);
+}
+
+TS_API int ts_paged_attention_bf16_sigmoid(const void* q, long long q_stride, void* out, const void* k_pool,
+                                           const void* v_pool, long long page_stride, long long entry_offset,
+                                           int page_tokens, int num_pages, const int* block_table, int table_width,
+                                           const int* cu_q, const int* ctx_lens, int num_seqs, int max_q_len,
+                                           int min_q_len, int max_ctx_len, int nh, int nkv, int hd, float scale, int window,
+                                           float* scratch, long long scratch_floats, const int* prefill_seqs,
+                                           int num_prefill_seqs, const float* slopes, const float* head_bias,
+                                           const void* gate, long long gate_stride, cudaStream_t stream) {
+    TS_REQUIRE(q_stride % 8 == 0 && (uintptr_t)q % 16 == 0, "paged_attention_bf16: query rows must start on 16-byte boundaries");
+    return run(q, q_stride, out, k_pool, v_pool, page_stride, entry_offset, page_tokens, num_pages, block_table, table_width,
+               cu_q, ctx_lens, num_seqs, max_q_len, min_q_len, max_ctx_len, nh, nkv, hd, scale, window, scratch,
+               scratch_floats, prefill_seqs, num_prefill_seqs, true, slopes, head_bias, gate, gate_stride, stream);
 }

@@ -26,6 +26,17 @@ int ts_paged_attention_bf16(const void* qkv, void* out, const void* k_pool, cons
                             float* scratch, long long scratch_floats, const int* prefill_seqs, int num_prefill_seqs,
                             cudaStream_t stream);
 
+// The same kernels with sigmoid weights: a visible key's weight is sigmoid(score * scale - slopes[h] (i - j) +
+// head_bias[h]), nothing is normalised over the keys, and head h's output is multiplied by sigmoid(gate[t, h])
+// (null pointers: the term is absent).  Queries in a matrix of their own, q_stride elements a row.
+int ts_paged_attention_bf16_sigmoid(const void* q, long long q_stride, void* out, const void* k_pool, const void* v_pool,
+                                    long long page_stride, long long entry_offset, int page_tokens, int num_pages,
+                                    const int* block_table, int table_width, const int* cu_q, const int* ctx_lens,
+                                    int num_seqs, int max_q_len, int min_q_len, int max_ctx_len, int nh, int nkv, int hd,
+                                    float scale, int window, float* scratch, long long scratch_floats,
+                                    const int* prefill_seqs, int num_prefill_seqs, const float* slopes,
+                                    const float* head_bias, const void* gate, long long gate_stride, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

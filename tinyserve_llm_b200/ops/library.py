@@ -29,6 +29,7 @@ _SIGNATURES = {
     "ts_attention_bf16_supported": ("int", "iiii"),
     "ts_paged_attention_bf16": ("int", "pppplliipippiiiiiiifiplpip"),
     "ts_paged_attention_generic": ("int", "pppplliipippiiiifiip"),
+    "ts_paged_attention_bf16_sigmoid": ("int", "pl" "ppp" "lliipippiiiiiiifiplpi" "pppl" "p"),
     "ts_attention_tcgen05_supported": ("int", "iiiii"),
     "ts_prefill_attention_tcgen05": ("int", "ppppiiiipippiiiiiifpipp"),
     "ts_embedding": ("int", "pppiiiip"),
@@ -618,6 +619,29 @@ class Ops:
                                       or tuple(head_gate.shape) != (q.shape[0], nh)):
             raise KernelError("paged_attention_split: the head gate must be a [T, heads] stretch of the activation dtype")
         out = torch.empty((q.shape[0], nh * vd), dtype=q.dtype, device=q.device)
+        if (weights == "sigmoid" and hd == vd and q.dtype == torch.bfloat16 and getattr(ctx, "cu_q", None) is not None
+                and q.stride(0) % 8 == 0 and self.lib.ts_attention_bf16_supported(hd, binding.page_tokens, nh, nkv)):
+            # the tensor-core kernels: tiles of a prompt's portion, split keys for requests that feed one token
+            num_seqs = ctx.ctx_lens.shape[0]
+            prefill_seqs = getattr(ctx, "prefill_seqs", None)
+            num_prefill = prefill_seqs.shape[0] if prefill_seqs is not None else 0
+            decode_ctx = getattr(ctx, "max_decode_ctx_len", ctx.max_ctx_len)
+            scratch, floats = None, 0
+            if ctx.min_q_len <= 1:
+                floats = self.lib.ts_attention_bf16_scratch_floats(num_seqs, nh, hd, decode_ctx)
+                key = ("attention", floats)
+                scratch = ctx.scratch.get(key)
+                if scratch is None:
+                    scratch = ctx.scratch[key] = torch.empty((floats,), dtype=torch.float32, device=q.device)
+            self._call("ts_paged_attention_bf16_sigmoid", _ptr(q), q.stride(0), _ptr(out), _ptr(binding.k_pool),
+                       _ptr(binding.v_pool), binding.page_stride, binding.entry_offset, binding.page_tokens,
+                       binding.num_pages, _ptr(binding.block_table), binding.table_width, _ptr(ctx.cu_q),
+                       _ptr(ctx.ctx_lens), num_seqs, ctx.max_q_len, ctx.min_q_len, decode_ctx, nh, nkv, hd, scale, window,
+                       _ptr(scratch), floats, _ptr(prefill_seqs), num_prefill, _ptr(slopes), _ptr(head_bias),
+                       _ptr(head_gate), head_gate.stride(0) if head_gate is not None else 0, _stream())
+            if ctx.min_q_len <= 1:
+                self.launches += 1 if ctx.max_q_len <= 1 else 2      # decode + combine (+ prefill) in one call
+            return out
         v_page_stride, v_entry_offset = binding.value_geometry()
         self._call("ts_paged_attention_scored", _ptr(q), q.stride(0), _ptr(out), _ptr(binding.k_pool), _ptr(binding.v_pool),
                    binding.page_stride, binding.entry_offset, v_page_stride, v_entry_offset, binding.page_tokens,
