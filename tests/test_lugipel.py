@@ -297,14 +297,15 @@ def test_a_key_at_a_page_border_is_seen_to_the_windows_edge_and_no_further(dtype
     torch.testing.assert_close(portion, want, **TOL[dtype])
 
 
+@pytest.mark.parametrize("prompt_kernel", ["tcgen05", "mma"])
 @pytest.mark.parametrize("heads, kv_heads, dim, window", [(4, 2, 64, 100), (6, 1, 128, 257), (2, 2, 64, 1000), (16, 2, 128, 64)])
-def test_sigmoid_attention_at_the_tensor_core_kernels_sizes(heads, kv_heads, dim, window):
+def test_sigmoid_attention_at_the_tensor_core_kernels_sizes(monkeypatch, heads, kv_heads, dim, window, prompt_kernel):
     """
     Keys and values of 64 and of 128 channels a head on pages of 64 tokens in bfloat16: a prompt's portions run in
     tiles of 64 queries against tiles of 64 keys, single tokens in splits of 256 keys that are merged.  Two
     requests of unequal length, in portions that end inside tiles, with windows that begin inside a tile, at
     its edge and before the first key, then token by token across a split's edge; a portion beside single
-    tokens in one step.
+    tokens in one step.  The portions once on the tcgen05 kernel (tiles of 128 queries), once on the mma one.
     """
     dtype, width = torch.bfloat16, 64
     spec, m = _attention_spec(width, heads, kv_heads, dim, dim, 0.2, window, 0.3, 50)
@@ -313,6 +314,7 @@ def test_sigmoid_attention_at_the_tensor_core_kernels_sizes(heads, kv_heads, dim
         t["pb"] = torch.linspace(-3.0, -1.0, heads).to(t["pb"].dtype)
 
     mixer, w = _mixer(spec, dtype, 7, edit)
+    monkeypatch.setattr(mixer.rt.ops, "tcgen05_attention", prompt_kernel == "tcgen05")
     g = torch.Generator().manual_seed(3)
     lens = [530, 203]
     x_of = [torch.randn(n, width, generator=g).to(dtype) for n in lens]
@@ -324,7 +326,8 @@ def test_sigmoid_attention_at_the_tensor_core_kernels_sizes(heads, kv_heads, dim
         rows_close(a, b, dtype)
 
 
-def test_a_far_key_stands_out_through_the_tensor_core_kernels():
+@pytest.mark.parametrize("prompt_kernel", ["tcgen05", "mma"])
+def test_a_far_key_stands_out_through_the_tensor_core_kernels(monkeypatch, prompt_kernel):
     """
     As the test at a page's border, at head sizes the tensor-core kernels take: one key at the last slot of a
     page of 64 tokens weighs nearly 1, every other next to nothing; queries see it up to window - 1 positions
@@ -346,6 +349,7 @@ def test_a_far_key_stands_out_through_the_tensor_core_kernels():
         t["g"] = torch.zeros_like(t["g"])
 
     mixer, w = _mixer(spec, dtype, 5, edit)
+    monkeypatch.setattr(mixer.rt.ops, "tcgen05_attention", prompt_kernel == "tcgen05")
     g = torch.Generator().manual_seed(2)
     n = far + window + 40
     x = torch.randn(n, width, generator=g) * 0.3

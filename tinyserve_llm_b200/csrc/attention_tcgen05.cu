@@ -152,6 +152,17 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
+// 2^x for any x (+inf above the float range) and 1 / x (0 for +inf): one instruction each.
+__device__ __forceinline__ float fast_exp2_any(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float fast_rcp(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -179,9 +190,18 @@ struct FlashParams {
     int entries, entry;               // cache entries of the layer group; this layer's index among them
     float scale_log2;
     int* error;
+    // sigmoid weights (the SIG kernel): a window, terms of the score and the output gate; a null pointer: the term is absent
+    int window;                       // a query at position p sees keys p - window + 1 .. p (0: all up to p)
+    const float* slopes;              // [nh]: slopes[h] * (position - key) is taken off the score
+    const float* head_bias;           // [nh]: added to every score of the head
+    const __nv_bfloat16* gate;        // [T, nh] logits, gate_stride elements a row: the head's output times their sigmoid
+    long long gate_stride;
 };
 
-template <int HD>
+// SIG: a visible key's weight is sigmoid(score * scale - slope (position - key) + bias): no maximum, no sum, no
+// rescaling, nothing exchanged between the two threads of a row; the epilogue multiplies by the head's gate.
+// Only this form takes a window: its first key tile is the one that holds the first key the tile's first query sees.
+template <int HD, bool SIG>
 __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                         const __grid_constant__ CUtensorMap map_k,
                                                                         const __grid_constant__ CUtensorMap map_v,
@@ -213,6 +233,8 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
     const int pos0 = ctx - q_len + row0;             // position of the tile's first query
     const int last_pos = pos0 + rows - 1;
     const int num_kv = last_pos / KEYS + 1;
+    const int first_seen = SIG && p.window > 0 ? max(0, pos0 - p.window + 1) : 0;     // the first key any row of the tile sees
+    const int kv_begin = first_seen / KEYS;          // tiles kv_begin .. num_kv - 1; `it` counts them from 0 for stages and parities
     const int kvh = head / (p.nh / p.nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* table = p.block_table + (long long)seq * p.table_width;
@@ -251,9 +273,9 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
         mbar_expect_tx(&q_full, Q_BYTES);
 #pragma unroll
         for (int h = 0; h < SUBS; ++h) tma_load_2d(q_tile + h * SUB_Q, &map_q, &q_full, head * HD + h * 64, q_begin + row0);
-        for (int j = 0; j < num_kv; ++j) {
-            const int s = j & 1;
-            if (!mbar_wait(&stage_free[s], ((j >> 1) & 1) ^ 1, p.error, 11)) { failed = 1; break; }
+        for (int j = kv_begin; j < num_kv; ++j) {
+            const int it = j - kv_begin, s = it & 1;
+            if (!mbar_wait(&stage_free[s], ((it >> 1) & 1) ^ 1, p.error, 11)) { failed = 1; break; }
             unsigned char* k_tile = kv_tiles + s * STAGE_BYTES;
             unsigned char* v_tile = k_tile + KV_BYTES;
             mbar_expect_tx(&kv_full[s], STAGE_BYTES);
@@ -276,9 +298,9 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
         const uint32_t idesc_o = instr_desc(QROWS, 64, true);        // O in column blocks of 64 dims, one per sub-tile of V
         bool ok = mbar_wait(&q_full, 0, p.error, 12);
         // S = Q K^T of tile j, once its keys have landed
-        auto issue_scores = [&](int j) -> bool {
-            const int s = j & 1;
-            if (!mbar_wait(&kv_full[s], (j >> 1) & 1, p.error, 13)) return false;
+        auto issue_scores = [&](int it) -> bool {
+            const int s = it & 1;
+            if (!mbar_wait(&kv_full[s], (it >> 1) & 1, p.error, 13)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (int h = 0; h < SUBS; ++h) {
@@ -291,14 +313,15 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
             return true;
         };
         ok = ok && issue_scores(0);
-        for (int j = 0; j < num_kv && ok; ++j) {
+        const int num_it = num_kv - kv_begin;
+        for (int j = 0; j < num_it && ok; ++j) {       // j counts the tiles from the first one here
             const int s = j & 1;
             if (!mbar_wait(&p_ready, j & 1, p.error, 14)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             // The softmax has read S of tile j (P lies in columns of its own), so the next tile's scores go first:
             // its softmax can begin while O += P V of this tile is still running.  The softmax waits for that
             // product (stage_free) before it writes P again or rescales O.
-            if (j + 1 < num_kv && !issue_scores(j + 1)) { ok = false; break; }
+            if (j + 1 < num_it && !issue_scores(j + 1)) { ok = false; break; }
 #pragma unroll
             for (int h = 0; h < SUBS; ++h) {         // O += P V: 16 keys are 8 columns of packed P and 16 rows (2048 bytes) of a V sub-tile
                 const uint64_t v_desc = smem_desc(kv_tiles + s * STAGE_BYTES + KV_BYTES + h * SUB_KV);
@@ -322,27 +345,77 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
         constexpr int HK = KEYS / 2, HO = HD / 2;    // this thread's keys of a tile, and its dims of O
         const int col0 = half * HK;
         float m_run = -INFINITY, l_run = 0.f;
+        // SIG: the row's first visible key, and the score's terms that do not depend on the key, in powers of two
+        const int lo = SIG && p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        const float slope2 = SIG && p.slopes ? p.slopes[head] * LOG2E : 0.f;
+        const float bias2 = (SIG && p.head_bias ? p.head_bias[head] * LOG2E : 0.f) - slope2 * (float)pos;
         bool ok = true;
-        for (int j = 0; j < num_kv; ++j) {
-            const int s = j & 1;
+        for (int j = kv_begin; j < num_kv; ++j) {
+            const int it = j - kv_begin, s = it & 1;
             const int key0 = j * KEYS;
             // a wait that ran out: the warp (as one) skips the work of this and the later tiles but still meets its
             // partner at the barrier below and still arrives at p_ready, so that nobody is left waiting for it
-            if (ok && !mbar_wait(&s_done, j & 1, p.error, 15)) ok = false;
+            if (ok && !mbar_wait(&s_done, it & 1, p.error, 15)) ok = false;
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
-                pair_barrier(quadrant);
+                if (!SIG) pair_barrier(quadrant);
                 mbar_arrive(&p_ready);
                 continue;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const bool masked = key0 + KEYS - 1 > pos0;        // some row of the tile does not see all of these keys
+            // some row of the tile does not see all of these keys (beyond its own position, or before its window)
+            const bool masked = key0 + KEYS - 1 > pos0 || (SIG && p.window > 0 && key0 < last_pos - p.window + 1);
             // this thread's keys of S come into registers once, all loads under way together
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             uint32_t sv[HK / 32][32];
 #pragma unroll
             for (int ch = 0; ch < HK / 32; ++ch) tmem_ld32(lane_addr + col0 + ch * 32, sv[ch]);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if constexpr (SIG) {
+                // O += P V of the tile before must have retired before P is written again
+                if (it > 0 && !mbar_wait(&stage_free[(it - 1) & 1], ((it - 1) >> 1) & 1, p.error, 17)) ok = false;
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    mbar_arrive(&p_ready);
+                    continue;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int ch = 0; ch < HK / 32; ++ch) {
+                    const int c = col0 + ch * 32;
+                    const float term = fmaf(slope2, (float)(key0 + c), bias2);      // slope (key - position) + bias at the chunk's first key
+                    uint32_t packed[16];
+                    const uint32_t (&v)[32] = sv[ch];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        // weight = 1 / (1 + 2^-x): 2^-x is +inf for a hopeless key, and the weight 0
+                        const float x0 = fmaf(__uint_as_float(v[i]), p.scale_log2, fmaf(slope2, (float)i, term));
+                        const float x1 = fmaf(__uint_as_float(v[i + 1]), p.scale_log2, fmaf(slope2, (float)(i + 1), term));
+                        float w0 = fast_rcp(1.f + fast_exp2_any(-x0)), w1 = fast_rcp(1.f + fast_exp2_any(-x1));
+                        if (masked) {
+                            const int key = key0 + c + i;
+                            if (key > pos || key < lo) w0 = 0.f;
+                            if (key + 1 > pos || key + 1 < lo) w1 = 0.f;
+                        }
+                        packed[i >> 1] = pack_bf16(w0, w1);
+                    }
+                    tmem_st16(lane_addr + P_COL + (c >> 1), packed);
+                }
+                // value rows beyond the request's length, or before the first key the tile sees (their page may have been
+                // given back), hold whatever the page held: zero them before they are multiplied
+                if (half == 0 && r < KEYS && ((key0 + KEYS > ctx && key0 + r >= ctx) || key0 + r < first_seen)) {
+#pragma unroll
+                    for (int h = 0; h < SUBS; ++h) {
+                        unsigned char* v_row = kv_tiles + s * STAGE_BYTES + KV_BYTES + h * SUB_KV + r * 128;
+#pragma unroll
+                        for (int i = 0; i < 128; i += 16) *reinterpret_cast<uint4*>(v_row + i) = make_uint4(0, 0, 0, 0);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(&p_ready);
+            } else {
             // pass 1: the maximum over them (four running maxima: no long dependent chain)
 #pragma unroll
             for (int ch = 0; ch < HK / 32; ++ch) {
@@ -357,11 +430,11 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
                 }
             }
             float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            half_max[j & 1][half][r] = mx;
+            half_max[it & 1][half][r] = mx;
             pair_barrier(quadrant);
-            mx = fmaxf(mx, half_max[j & 1][half ^ 1][r]);
+            mx = fmaxf(mx, half_max[it & 1][half ^ 1][r]);
             // O += P V of the tile before must have retired before P is written again and O is rescaled
-            if (j > 0 && !mbar_wait(&stage_free[(j - 1) & 1], ((j - 1) >> 1) & 1, p.error, 17)) ok = false;
+            if (it > 0 && !mbar_wait(&stage_free[(it - 1) & 1], ((it - 1) >> 1) & 1, p.error, 17)) ok = false;
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
                 mbar_arrive(&p_ready);
@@ -417,7 +490,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
             }
             l_run = l_run * corr + ((l4[0] + l4[1]) + (l4[2] + l4[3]));
             // this thread's dims of O follow the new reference; skipped when no row of the warp moved it
-            if (j > 0 && !__all_sync(0xffffffffu, corr == 1.f)) {
+            if (it > 0 && !__all_sync(0xffffffffu, corr == 1.f)) {
 #pragma unroll 1
                 for (int c = half * HO; c < half * HO + HO; c += 32) {
                     uint32_t v[32];
@@ -441,16 +514,20 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(&p_ready);
+            }
         }
         if (ok) ok = mbar_wait(&all_done, 0, p.error, 16);
         ok = __all_sync(0xffffffffu, ok);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         // the row's sum is the two halves' sums (both were kept against the same maxima)
-        half_sum[half][r] = l_run;
-        pair_barrier(quadrant);
-        l_run += half_sum[half ^ 1][r];
+        if (!SIG) {
+            half_sum[half][r] = l_run;
+            pair_barrier(quadrant);
+            l_run += half_sum[half ^ 1][r];
+        }
         if (ok && !failed) {                         // every thread of the warp takes part in the loads; only real rows store
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            if (SIG) inv = (p.gate && r < rows) ? 1.f / (1.f + __expf(-__bfloat162float(p.gate[(long long)(q_begin + row0 + r) * p.gate_stride + head]))) : 1.f;
             __nv_bfloat16* o = p.out + ((long long)(q_begin + row0 + r) * p.nh + head) * HD;
 #pragma unroll 1
             for (int c = half * HO; c < half * HO + HO; c += 32) {
@@ -516,19 +593,20 @@ TS_API int ts_attention_tcgen05_supported(int hd, int page_tokens, int nh, int n
     return (hd == 64 || hd == 128) && page_tokens % 64 == 0 && nkv > 0 && nh % nkv == 0 && window == 0;
 }
 
-// Prompt portions (requests that feed more than one token) of a step; requests that feed one token
-// are left to the decode kernels.  prefill_seqs (optional, device) lists the former, so that the grid
-// has no CTAs for the latter.  The pools are [pages][entries][kv heads][page_tokens][64].
-TS_API int ts_prefill_attention_tcgen05(const void* qkv, void* out, const void* k_pool, const void* v_pool, int num_pages,
-                                        int entries, int entry, int page_tokens, const int* block_table, int table_width,
-                                        const int* cu_q, const int* ctx_lens, int num_seqs, int num_tokens, int max_q_len,
-                                        int nh, int nkv, int hd, float scale, const int* prefill_seqs, int num_prefill_seqs,
-                                        int* error, cudaStream_t stream) {
+namespace {
+
+int run_prefill(const void* q, long long q_cols, long long q_stride, void* out, const void* k_pool, const void* v_pool,
+                int num_pages, int entries, int entry, int page_tokens, const int* block_table, int table_width,
+                const int* cu_q, const int* ctx_lens, int num_seqs, int num_tokens, int max_q_len, int nh, int nkv, int hd,
+                float scale, const int* prefill_seqs, int num_prefill_seqs, int* error, bool sigmoid, int window,
+                const float* slopes, const float* head_bias, const void* gate, long long gate_stride, cudaStream_t stream) {
     TS_REQUIRE(ts_attention_tcgen05_supported(hd, page_tokens, nh, nkv, 0), "attention_tcgen05: sizes not taken (head_dim %d, page %d)", hd, page_tokens);
+    TS_REQUIRE(sigmoid || window == 0, "attention_tcgen05: only the sigmoid form takes a window");
+    TS_REQUIRE(window >= 0, "attention_tcgen05: a negative window");
     TS_REQUIRE(error != nullptr, "attention_tcgen05: an error word is needed");
     TS_REQUIRE(num_seqs <= 65535 && (max_q_len + QROWS - 1) / QROWS <= 65535,
                "attention_tcgen05: more than 65535 requests, or tiles of a request, in a step");
-    TS_REQUIRE(((uintptr_t)qkv % 16 == 0) && ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0),
+    TS_REQUIRE(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0) && q_stride % 8 == 0,
                "attention_tcgen05: operands must be 16-byte aligned");
     if (num_seqs == 0 || max_q_len <= 1) return 0;
     TS_REQUIRE(prefill_seqs == nullptr || (num_prefill_seqs >= 0 && num_prefill_seqs <= num_seqs),
@@ -536,9 +614,8 @@ TS_API int ts_prefill_attention_tcgen05(const void* qkv, void* out, const void* 
     if (prefill_seqs != nullptr && num_prefill_seqs == 0) return 0;
     const long long pool_rows = (long long)num_pages * entries * nkv * page_tokens;
     TS_REQUIRE(pool_rows < 0x7fffffffll, "attention_tcgen05: the pool has too many rows for 32-bit TMA coordinates");
-    const long long row_width = (long long)(nh + 2 * nkv) * hd;
     CUtensorMap map_q, map_k, map_v;
-    if (make_map(&map_q, qkv, num_tokens, row_width, row_width, QROWS)) return 1;
+    if (make_map(&map_q, q, num_tokens, q_cols, q_stride, QROWS)) return 1;
     if (make_map(&map_k, k_pool, pool_rows, hd, hd, 64)) return 1;
     if (make_map(&map_v, v_pool, pool_rows, hd, hd, 64)) return 1;
     FlashParams p;
@@ -556,17 +633,56 @@ TS_API int ts_prefill_attention_tcgen05(const void* qkv, void* out, const void* 
     p.entry = entry;
     p.scale_log2 = scale * LOG2E;
     p.error = error;
+    p.window = window;
+    p.slopes = slopes;
+    p.head_bias = head_bias;
+    p.gate = (const __nv_bfloat16*)gate;
+    p.gate_stride = gate_stride;
     dim3 grid(nh, (max_q_len + QROWS - 1) / QROWS, prefill_seqs ? num_prefill_seqs : num_seqs);
-    if (hd == 64) {
-        const size_t smem = (size_t)Shape<64>::Q_BYTES + 2 * Shape<64>::STAGE_BYTES + 1024;
-        auto kernel = prefill_attention_tcgen05_kernel<64>;
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        TS_CHAINED_CHECK("attention_tcgen05", launch_chained(kernel, grid, dim3(THREADS), smem, stream, map_q, map_k, map_v, p));
-    } else {
-        const size_t smem = (size_t)Shape<128>::Q_BYTES + 2 * Shape<128>::STAGE_BYTES + 1024;
-        auto kernel = prefill_attention_tcgen05_kernel<128>;
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        TS_CHAINED_CHECK("attention_tcgen05", launch_chained(kernel, grid, dim3(THREADS), smem, stream, map_q, map_k, map_v, p));
-    }
+#define TS_FLASH_LAUNCH(HD, SIG)                                                                                          \
+    do {                                                                                                                  \
+        const size_t smem = (size_t)Shape<HD>::Q_BYTES + 2 * Shape<HD>::STAGE_BYTES + 1024;                               \
+        auto kernel = prefill_attention_tcgen05_kernel<HD, SIG>;                                                          \
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                             \
+        TS_CHAINED_CHECK("attention_tcgen05", launch_chained(kernel, grid, dim3(THREADS), smem, stream, map_q, map_k, map_v, p)); \
+    } while (0)
+    if (hd == 64 && sigmoid) TS_FLASH_LAUNCH(64, true);
+    else if (hd == 64) TS_FLASH_LAUNCH(64, false);
+    else if (sigmoid) TS_FLASH_LAUNCH(128, true);
+    else TS_FLASH_LAUNCH(128, false);
+#undef TS_FLASH_LAUNCH
     return 0;
+}
+
+}  // namespace
+
+// Prompt portions (requests that feed more than one token) of a step; requests that feed one token
+// are left to the decode kernels.  prefill_seqs (optional, device) lists the former, so that the grid
+// has no CTAs for the latter.  The pools are [pages][entries][kv heads][page_tokens][64].
+TS_API int ts_prefill_attention_tcgen05(const void* qkv, void* out, const void* k_pool, const void* v_pool, int num_pages,
+                                        int entries, int entry, int page_tokens, const int* block_table, int table_width,
+                                        const int* cu_q, const int* ctx_lens, int num_seqs, int num_tokens, int max_q_len,
+                                        int nh, int nkv, int hd, float scale, const int* prefill_seqs, int num_prefill_seqs,
+                                        int* error, cudaStream_t stream) {
+    const long long row_width = (long long)(nh + 2 * nkv) * hd;
+    return run_prefill(qkv, row_width, row_width, out, k_pool, v_pool, num_pages, entries, entry, page_tokens, block_table,
+                       table_width, cu_q, ctx_lens, num_seqs, num_tokens, max_q_len, nh, nkv, hd, scale, prefill_seqs,
+                       num_prefill_seqs, error, false, 0, nullptr, nullptr, nullptr, 0, stream);
+}
+
+// The same with sigmoid weights: a visible key's weight is sigmoid(score * scale - slopes[h] (i - j) + head_bias[h]),
+// nothing is normalised over the keys, query i sees keys i - window + 1 .. i (window 0: all up to i), and head h's
+// output is multiplied by sigmoid(gate[t, h]) (null pointers: the term is absent).  Queries [T, nh * hd] in a matrix
+// of their own, q_stride elements a row.
+TS_API int ts_prefill_attention_tcgen05_sigmoid(const void* q, long long q_stride, void* out, const void* k_pool,
+                                                const void* v_pool, int num_pages, int entries, int entry, int page_tokens,
+                                                const int* block_table, int table_width, const int* cu_q,
+                                                const int* ctx_lens, int num_seqs, int num_tokens, int max_q_len, int nh,
+                                                int nkv, int hd, float scale, int window, const float* slopes,
+                                                const float* head_bias, const void* gate, long long gate_stride,
+                                                const int* prefill_seqs, int num_prefill_seqs, int* error,
+                                                cudaStream_t stream) {
+    return run_prefill(q, (long long)nh * hd, q_stride, out, k_pool, v_pool, num_pages, entries, entry, page_tokens,
+                       block_table, table_width, cu_q, ctx_lens, num_seqs, num_tokens, max_q_len, nh, nkv, hd, scale,
+                       prefill_seqs, num_prefill_seqs, error, true, window, slopes, head_bias, gate, gate_stride, stream);
 }

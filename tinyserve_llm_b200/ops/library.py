@@ -32,6 +32,7 @@ _SIGNATURES = {
     "ts_paged_attention_bf16_sigmoid": ("int", "pl" "ppp" "lliipippiiiiiiifiplpi" "pppl" "p"),
     "ts_attention_tcgen05_supported": ("int", "iiiii"),
     "ts_prefill_attention_tcgen05": ("int", "ppppiiiipippiiiiiifpipp"),
+    "ts_prefill_attention_tcgen05_sigmoid": ("int", "pl" "ppp" "iiiipippiiiiiifi" "pppl" "pipp"),
     "ts_embedding": ("int", "pppiiiip"),
     "ts_feed_tokens": ("int", "pipip"),
     "ts_gemm_tcgen05_supported": ("int", "ppiiil"),
@@ -627,6 +628,21 @@ class Ops:
             num_prefill = prefill_seqs.shape[0] if prefill_seqs is not None else 0
             decode_ctx = getattr(ctx, "max_decode_ctx_len", ctx.max_ctx_len)
             scratch, floats = None, 0
+            max_q_len = ctx.max_q_len
+            gate_stride = head_gate.stride(0) if head_gate is not None else 0
+            if (max_q_len > 1 and self.tcgen05_attention and self.lib.ts_attention_tcgen05_supported(
+                    hd, binding.page_tokens, nh, nkv, 0)):
+                # prompt portions on the tcgen05 kernel; requests that feed one token stay with the split-key kernels
+                per_entry = nkv * binding.page_tokens * hd
+                self._call("ts_prefill_attention_tcgen05_sigmoid", _ptr(q), q.stride(0), _ptr(out), _ptr(binding.k_pool),
+                           _ptr(binding.v_pool), binding.num_pages, binding.page_stride // per_entry,
+                           binding.entry_offset // per_entry, binding.page_tokens, _ptr(binding.block_table),
+                           binding.table_width, _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), num_seqs, q.shape[0], max_q_len, nh, nkv,
+                           hd, scale, window, _ptr(slopes), _ptr(head_bias), _ptr(head_gate), gate_stride,
+                           _ptr(prefill_seqs), num_prefill, self.error_word().data_ptr(), _stream())
+                if ctx.min_q_len > 1:
+                    return out
+                max_q_len = 1
             if ctx.min_q_len <= 1:
                 floats = self.lib.ts_attention_bf16_scratch_floats(num_seqs, nh, hd, decode_ctx)
                 key = ("attention", floats)
@@ -636,11 +652,11 @@ class Ops:
             self._call("ts_paged_attention_bf16_sigmoid", _ptr(q), q.stride(0), _ptr(out), _ptr(binding.k_pool),
                        _ptr(binding.v_pool), binding.page_stride, binding.entry_offset, binding.page_tokens,
                        binding.num_pages, _ptr(binding.block_table), binding.table_width, _ptr(ctx.cu_q),
-                       _ptr(ctx.ctx_lens), num_seqs, ctx.max_q_len, ctx.min_q_len, decode_ctx, nh, nkv, hd, scale, window,
-                       _ptr(scratch), floats, _ptr(prefill_seqs), num_prefill, _ptr(slopes), _ptr(head_bias),
-                       _ptr(head_gate), head_gate.stride(0) if head_gate is not None else 0, _stream())
+                       _ptr(ctx.ctx_lens), num_seqs, max_q_len, min(ctx.min_q_len, max_q_len), decode_ctx, nh, nkv, hd,
+                       scale, window, _ptr(scratch), floats, _ptr(prefill_seqs), num_prefill, _ptr(slopes),
+                       _ptr(head_bias), _ptr(head_gate), gate_stride, _stream())
             if ctx.min_q_len <= 1:
-                self.launches += 1 if ctx.max_q_len <= 1 else 2      # decode + combine (+ prefill) in one call
+                self.launches += 1 if max_q_len <= 1 else 2          # decode + combine (+ prefill) in one call
             return out
         v_page_stride, v_entry_offset = binding.value_geometry()
         self._call("ts_paged_attention_scored", _ptr(q), q.stride(0), _ptr(out), _ptr(binding.k_pool), _ptr(binding.v_pool),
