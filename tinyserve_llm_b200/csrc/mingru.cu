@@ -26,18 +26,25 @@ struct MinGRUArgs {
     void* out; int width;
 };
 
-__device__ __forceinline__ float mingru_sigmoid(float x) { return 1.f / (1.f + expf(-x)); }
+// FAST (outputs of 16 bits): the exponential and the division by their one-instruction forms, whose error of a
+// few units in the last place of a float is far below the output's rounding; float32 outputs keep the exact ones.
+template <bool FAST>
+__device__ __forceinline__ float mingru_sigmoid(float x) {
+    return FAST ? __fdividef(1.f, 1.f + __expf(-x)) : 1.f / (1.f + expf(-x));
+}
 
+template <bool FAST>
 __device__ __forceinline__ void mingru_gates(float a, float u, float bz, float bx, float& z, float& c) {
-    z = mingru_sigmoid(a + bz);
+    z = mingru_sigmoid<FAST>(a + bz);
     const float v = u + bx;
-    c = v >= 0.f ? v + 0.5f : mingru_sigmoid(v);
+    c = v >= 0.f ? v + 0.5f : mingru_sigmoid<FAST>(v);
 }
 
 constexpr int MG_AHEAD = 4;
 
 template <typename TY, typename T>
 __global__ void __launch_bounds__(128) mingru_scan_kernel(MinGRUArgs p) {
+    constexpr bool FAST = sizeof(T) == 2;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int s = blockIdx.y;
     if (c >= p.width) return;
@@ -66,9 +73,9 @@ __global__ void __launch_bounds__(128) mingru_scan_kernel(MinGRUArgs p) {
         for (int i = 0; i < MG_AHEAD; ++i) {
             if (t + i < t1) {
                 float z, cand;
-                mingru_gates(a[i], u[i], bz, bx, z, cand);
+                mingru_gates<FAST>(a[i], u[i], bz, bx, z, cand);
                 S = (1.f - z) * S + z * cand;
-                out[(long long)(t + i) * p.width + c] = from_float<T>(S * (g[i] * mingru_sigmoid(g[i])));
+                out[(long long)(t + i) * p.width + c] = from_float<T>(S * (g[i] * mingru_sigmoid<FAST>(g[i])));
             }
         }
 #pragma unroll
@@ -77,10 +84,12 @@ __global__ void __launch_bounds__(128) mingru_scan_kernel(MinGRUArgs p) {
     *sp = S;
 }
 
-constexpr int MG_WARPS = 16;
+constexpr int MG_WARPS = 32;
+constexpr int MG_BATCH = 8;              // tokens whose loads are under way together
 
 template <typename TY, typename T>
 __global__ void __launch_bounds__(MG_WARPS * 32) mingru_scan_chunked_kernel(MinGRUArgs p) {
+    constexpr bool FAST = sizeof(T) == 2;
     __shared__ float As[MG_WARPS][32], Bs[MG_WARPS][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int c = blockIdx.x * 32 + lane;
@@ -96,13 +105,22 @@ __global__ void __launch_bounds__(MG_WARPS * 32) mingru_scan_chunked_kernel(MinG
     const TY* y = (const TY*)p.y;
     // first walk: the stretch as one step S_end = A S_begin + B
     float A = 1.f, B = 0.f;
-#pragma unroll 4
-    for (int t = w0; t < w1; ++t) {
-        const long long row = (long long)t * p.y_stride + cc;
-        float z, cand;
-        mingru_gates(to_float<TY>(y[row + p.z_off]), to_float<TY>(y[row + p.x_off]), bz, bx, z, cand);
-        A *= 1.f - z;
-        B = (1.f - z) * B + z * cand;
+    for (int t = w0; t < w1; t += MG_BATCH) {
+        float a[MG_BATCH], u[MG_BATCH];
+#pragma unroll
+        for (int i = 0; i < MG_BATCH; ++i) {                 // rows beyond the stretch: its last row again, not used
+            const long long row = (long long)min(t + i, w1 - 1) * p.y_stride + cc;
+            a[i] = to_float<TY>(y[row + p.z_off]); u[i] = to_float<TY>(y[row + p.x_off]);
+        }
+#pragma unroll
+        for (int i = 0; i < MG_BATCH; ++i) {
+            if (t + i < w1) {
+                float z, cand;
+                mingru_gates<FAST>(a[i], u[i], bz, bx, z, cand);
+                A *= 1.f - z;
+                B = (1.f - z) * B + z * cand;
+            }
+        }
     }
     As[warp][lane] = A;
     Bs[warp][lane] = B;
@@ -111,14 +129,22 @@ __global__ void __launch_bounds__(MG_WARPS * 32) mingru_scan_chunked_kernel(MinG
     float S = *sp;
     for (int w = 0; w < warp; ++w) S = As[w][lane] * S + Bs[w][lane];      // the state this warp's stretch starts from
     T* out = (T*)p.out;
-#pragma unroll 4
-    for (int t = w0; t < w1; ++t) {
-        const long long row = (long long)t * p.y_stride + cc;
-        float z, cand;
-        mingru_gates(to_float<TY>(y[row + p.z_off]), to_float<TY>(y[row + p.x_off]), bz, bx, z, cand);
-        const float g = to_float<TY>(y[row + p.g_off]);
-        S = (1.f - z) * S + z * cand;
-        if (live) out[(long long)t * p.width + c] = from_float<T>(S * (g * mingru_sigmoid(g)));
+    for (int t = w0; t < w1; t += MG_BATCH) {
+        float a[MG_BATCH], u[MG_BATCH], g[MG_BATCH];
+#pragma unroll
+        for (int i = 0; i < MG_BATCH; ++i) {
+            const long long row = (long long)min(t + i, w1 - 1) * p.y_stride + cc;
+            a[i] = to_float<TY>(y[row + p.z_off]); u[i] = to_float<TY>(y[row + p.x_off]); g[i] = to_float<TY>(y[row + p.g_off]);
+        }
+#pragma unroll
+        for (int i = 0; i < MG_BATCH; ++i) {
+            if (t + i < w1) {
+                float z, cand;
+                mingru_gates<FAST>(a[i], u[i], bz, bx, z, cand);
+                S = (1.f - z) * S + z * cand;
+                if (live) out[(long long)(t + i) * p.width + c] = from_float<T>(S * (g[i] * mingru_sigmoid<FAST>(g[i])));
+            }
+        }
     }
     if (live && warp == MG_WARPS - 1) *sp = S;               // the last warp ends at the request's last token (or holds the state unchanged)
 }
@@ -134,7 +160,7 @@ TS_API int ts_mingru_scan(const void* y, long long y_stride, int z_off, int x_of
     TS_REQUIRE(y_dtype == TS_F32 || y_dtype == dtype, "mingru_scan: the projections are float32 or of the activation dtype");
     if (num_seqs == 0 || num_tokens == 0) return 0;
     MinGRUArgs p{y, y_stride, z_off, x_off, g_off, z_bias, x_bias, cu_q, state_slots, num_seqs, state, state_stride, out, width};
-    const bool chunked = max_q_len >= 8 * MG_WARPS;
+    const bool chunked = max_q_len >= 4 * MG_WARPS;
     const dim3 grid(chunked ? (width + 31) / 32 : (width + 127) / 128, num_seqs);
     const int threads = chunked ? MG_WARPS * 32 : 128;
 #define TS_MINGRU(TY, T)                                                                   \
