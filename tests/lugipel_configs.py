@@ -18,6 +18,11 @@ def attention(heads, kv_heads, dim, vdim, scale, window, coef, every):
                                            "mask": {"size": window}, "q_temp": {"coef": coef, "every": every}}}
 
 
+def open_attention(heads, kv_heads, dim, vdim, scale):
+    """Neither `mask` nor `q_temp`: every earlier key is seen, the queries keep their length."""
+    return {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}}
+
+
 def dense(ff):
     return {"kind": "dense", "ff": ff}
 
@@ -49,11 +54,12 @@ RECURRENT = model(211, 64, 1e-6, 1.0, [
     (mingru(33), dense(50)),
 ])
 
-# attention layers only, a window longer than every prompt of the tests and one of a single token
+# attention layers only, a window longer than every prompt of the tests, one of a single token and a layer without one
 WINDOWS = model(128, 80, 1e-6, 4.0, [
     (attention(5, 5, 24, 12, 0.2, 1000, 0.5, 16), dense(96)),
     (attention(2, 1, 32, 64, 0.15, 1, 0.1, 3), moe(8, 0, 2, 16, groups=(4, 2), scale=3.0)),
     (attention(4, 2, 8, 24, 0.4, 64, 0.3, 64), dense(40)),
+    (open_attention(3, 1, 16, 20, 0.22), None),
 ])
 
 # sizes the bfloat16 kernels for a few tokens and the tensor-core attention take: widths that are multiples of 32,
@@ -63,6 +69,7 @@ WIDE = model(512, 128, 1e-6, 2.0, [
     (mingru(160), dense(192)),
     (attention(6, 2, 128, 128, 0.09, 70, 0.25, 10), moe(6, 0, 3, 32, groups=(2, 2), scale=1.0)),
     (attention(2, 2, 64, 64, 0.11, 300, 0.0, 1), dense(64)),
+    (open_attention(4, 1, 64, 64, 0.1), None),
 ])
 
 WEIGHTS = {"std": 0.08, "unit_std": 0.25}

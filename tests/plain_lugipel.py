@@ -72,12 +72,13 @@ def sigmoid_attention(h: torch.Tensor, w: dict, m: dict, eps: float, start: int 
     """A whole sequence (positions start, start + 1, ...) with nothing before it.  h [T, width]."""
     T = h.shape[0]
     H, G, D, V = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
-    window = int(m["mask"]["size"])
+    window = int(m["mask"]["size"]) if m.get("mask") is not None else T + start + 1     # no mask: every earlier key
     pos = torch.arange(start, start + T)
     q = rms_norm((h @ w["q"].T).view(T, H, D), w["q.norm"], eps)
     k = rms_norm((h @ w["k"].T).view(T, G, D), w["k.norm"], eps)
     v = (h @ w["v"].T).view(T, G, V)
-    q = q * query_temperature(pos, float(m["q_temp"]["coef"]), int(m["q_temp"]["every"]))[:, None, None]
+    if m.get("q_temp") is not None:
+        q = q * query_temperature(pos, float(m["q_temp"]["coef"]), int(m["q_temp"]["every"]))[:, None, None]
     gate = torch.sigmoid(h @ w["g"].T)                                    # [T, H]
     dist = (pos[:, None] - pos[None, :]).to(F64)                          # i - j
     seen = (dist >= 0) & (dist < window)

@@ -52,7 +52,7 @@ def test_declared_tensors_follow_the_layers():
 @pytest.mark.parametrize("edit, word", [
     (lambda c: c["layers"][0].update(type="conv"), "type"),
     (lambda c: c["layers"][0]["mixer"].update(heads=5), "kv_heads"),
-    (lambda c: c["layers"][0]["mixer"].pop("mask"), "mask.size"),
+    (lambda c: c["layers"][0]["mixer"]["mask"].pop("size"), "mask.size"),
     (lambda c: c["layers"][0]["mixer"]["q_temp"].update(every=0), "q_temp.every"),
     (lambda c: c["layers"][1]["mlp"].update(kind="glu"), "kind"),
     (lambda c: c["layers"][0]["mlp"]["router"]["groups"].update(count=2), "groups"),
@@ -68,6 +68,23 @@ def test_what_cannot_be_served_is_refused_with_the_key(edit, word):
     edit(raw)
     with pytest.raises(ConfigError, match=word):
         LugipelConfig.from_dict(raw)
+
+
+def test_a_mixer_without_window_or_temperature_has_neither():
+    raw = copy.deepcopy(C.MIXED)
+    raw["layers"][0]["mixer"].pop("mask")
+    raw["layers"][0]["mixer"].pop("q_temp")
+    a = lugipel_model_spec(LugipelConfig.from_dict(raw)).blocks[0].mixer
+    assert a.window == 0 and a.q_temperature_every == 0
+
+
+def test_whole_numbers_serve_as_constants():
+    raw = copy.deepcopy(C.MIXED)
+    raw["layers"][0]["mixer"].update(scale=1)
+    raw["layers"][0]["mixer"]["q_temp"].update(coef=0)
+    raw["embedding"].update(scale=2)
+    spec = lugipel_model_spec(LugipelConfig.from_dict(raw))
+    assert spec.embedding_scale == 2.0 and spec.blocks[0].mixer.scale == 1.0 and spec.blocks[0].mixer.q_temperature_coef == 0.0
 
 
 @pytest.mark.parametrize("raw", [C.MIXED, C.RECURRENT, C.WINDOWS, C.WIDE])

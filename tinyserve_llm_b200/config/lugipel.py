@@ -120,10 +120,12 @@ class LugipelConfig:
         heads, kv_heads = _get(m, "heads", int), _get(m, "kv_heads", int)
         if heads % kv_heads:
             raise ConfigError(f"config.json: {where}.heads={heads} is not a multiple of kv_heads={kv_heads}")
-        coef, every = _get(m, "q_temp.coef", float), _get(m, "q_temp.every", int)
+        # a mixer without `q_temp` (or `mask`) has no query temperature (no window: every earlier key is seen)
+        coef, every = (_get(m, "q_temp.coef", float), _get(m, "q_temp.every", int)) if m.get("q_temp") is not None else (0.0, 0)
+        window = _get(m, "mask.size", int) if m.get("mask") is not None else 0
         return GatedAttentionSpec(hidden_size=self.width, num_heads=heads, num_kv_heads=kv_heads, head_dim=_get(m, "dim", int),
                                   value_dim=_get(m, "vdim", int), scale=_get(m, "scale", float),
-                                  window=_get(m, "mask.size", int), bias=False, qk_norm=True, qk_norm_eps=self.norm_eps,
+                                  window=window, bias=False, qk_norm=True, qk_norm_eps=self.norm_eps,
                                   qk_norm_scope="head", q_temperature_coef=coef, q_temperature_every=every,
                                   distance_slope_exponent=SLOPE_EXPONENT, head_bias=True, weights="sigmoid",
                                   output_gate=True, output_gate_scope="head", position=None)

@@ -83,14 +83,28 @@ TS_API int ts_moe_route(const float* logits, const float* bias, const int* seq_o
     return 0;
 }
 
-// Scores over all router outputs, choice inside the best groups (see the head of this file).  A warp a token;
-// every lane recomputes the scores it needs from the logits, so nothing but the groups' ranks is kept.
+// Scores over all router outputs, choice inside the best groups (see the head of this file).  A warp a token.
+// The scores and the choice scores are computed once into the warp's shared memory; every round of a choice
+// (the best group, the best output) is a walk of each lane over its own entries and two warp reductions: the
+// largest value as an ordered integer, then the lowest index among the lanes that hold it.
+__device__ __forceinline__ unsigned ordered_key(float x) {
+    const unsigned u = __float_as_uint(x + 0.f);          // -0 becomes +0: equal values, equal keys
+    return u & 0x80000000u ? ~u : u | 0x80000000u;
+}
+
+// (value, index) of the largest value over the warp, ties to the lower index; index 0x7fffffff: no lane had one
+__device__ __forceinline__ int warp_argmax(float best, int arg) {
+    const unsigned key = arg == 0x7fffffff ? 0u : ordered_key(best);
+    const unsigned top = __reduce_max_sync(0xffffffffu, key);
+    return (int)__reduce_min_sync(0xffffffffu, (unsigned)(key == top ? arg : 0x7fffffff));
+}
+
 __global__ void moe_route_grouped_kernel(const float* __restrict__ logits, const float* __restrict__ correction,
                                          const int* __restrict__ seq_of_token, int* __restrict__ chosen,
                                          float* __restrict__ share, int* __restrict__ counts, float* __restrict__ identity_share,
                                          int num_tokens, int outputs, int real_experts, int top, int groups, int keep,
                                          float weight_scale, float share_eps) {
-    extern __shared__ float group_rank[];                 // per warp: `groups` ranks, then `groups` flags (kept or not)
+    extern __shared__ float route_smem[];                 // per warp: scores, choice scores, groups' ranks, groups' flags
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + warp;
     if (t >= num_tokens) return;
@@ -99,22 +113,32 @@ __global__ void moe_route_grouped_kernel(const float* __restrict__ logits, const
         if (lane == 0 && identity_share) identity_share[t] = 0.f;
         return;
     }
-    float* rank = group_rank + (size_t)warp * 2 * groups;
+    float* score = route_smem + (size_t)warp * 2 * (outputs + groups);
+    float* choice = score + outputs;
+    float* rank = choice + outputs;
     int* kept = reinterpret_cast<int*>(rank + groups);
     const float* z = logits + (long long)t * outputs;
     float zmax = -INFINITY;
     for (int e = lane; e < outputs; e += 32) zmax = fmaxf(zmax, z[e]);
     zmax = warp_max(zmax);
     float sum = 0.f;
-    for (int e = lane; e < outputs; e += 32) sum += expf(z[e] - zmax);
+    for (int e = lane; e < outputs; e += 32) {
+        const float x = expf(z[e] - zmax);
+        score[e] = x;
+        sum += x;
+    }
     const float inv_sum = 1.f / warp_sum(sum);
-    auto score = [&](int e) { return expf(z[e] - zmax) * inv_sum; };
-    auto choice = [&](int e) { return score(e) + (correction ? correction[e] : 0.f); };
+    for (int e = lane; e < outputs; e += 32) {
+        const float x = score[e] * inv_sum;
+        score[e] = x;
+        choice[e] = x + (correction ? correction[e] : 0.f);
+    }
+    __syncwarp();
     const int per = outputs / groups;
     if (keep < groups) {
         for (int g = lane; g < groups; g += 32) {
             float m = -INFINITY;
-            for (int e = g * per; e < (g + 1) * per; ++e) m = fmaxf(m, choice(e));
+            for (int e = g * per; e < (g + 1) * per; ++e) m = fmaxf(m, choice[e]);
             rank[g] = m;
             kept[g] = 0;
         }
@@ -125,14 +149,9 @@ __global__ void moe_route_grouped_kernel(const float* __restrict__ logits, const
             for (int g = lane; g < groups; g += 32) {
                 if (kept[g]) continue;
                 const float x = rank[g];
-                if (x > best || (x == best && g < arg)) { best = x; arg = g; }
+                if (arg == 0x7fffffff || x > best) { best = x; arg = g; }
             }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-                const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
-                if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
-            }
+            arg = warp_argmax(best, arg);
             if (lane == 0 && arg != 0x7fffffff) kept[arg] = 1;
             __syncwarp();
         }
@@ -145,21 +164,16 @@ __global__ void moe_route_grouped_kernel(const float* __restrict__ logits, const
         for (int e = lane, i = 0; e < outputs; e += 32, ++i) {
             if (taken_lo >> i & 1) continue;
             if (keep < groups && !kept[e / per]) continue;
-            const float x = choice(e);
-            if (x > best || (x == best && e < arg)) { best = x; arg = e; }
+            const float x = choice[e];
+            if (arg == 0x7fffffff || x > best) { best = x; arg = e; }
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
-            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
-        }
+        arg = warp_argmax(best, arg);
         if (arg == 0x7fffffff) {                           // fewer outputs allowed than `top`: the choice stays empty
             if (lane == 0) { chosen[(long long)t * top + j] = -1; share[(long long)t * top + j] = 0.f; }
             continue;
         }
         if ((arg & 31) == lane) taken_lo |= 1ull << (arg >> 5);
-        const float w = score(arg);
+        const float w = score[arg];
         total += w;
         const bool real = arg < real_experts;
         if (!real) identity += w;
@@ -188,8 +202,9 @@ TS_API int ts_moe_route_grouped(const float* logits, const float* correction, co
                "moe_route: %d outputs in %d groups of which %d are kept", outputs, groups, keep);
     TS_REQUIRE(real_experts == outputs || identity_share, "moe_route: identity experts need a place for their shares");
     if (num_tokens <= 0) return 0;
-    const size_t smem = (size_t)4 * 2 * groups * sizeof(float);
-    moe_route_grouped_kernel<<<(num_tokens + 3) / 4, 128, smem, stream>>>(logits, correction, seq_of_token, chosen, share,
+    const size_t per_warp = (size_t)2 * (outputs + groups) * sizeof(float);           // at most 24 KB
+    const int warps = per_warp * 4 <= 48 * 1024 ? 4 : (per_warp * 2 <= 48 * 1024 ? 2 : 1);
+    moe_route_grouped_kernel<<<(num_tokens + warps - 1) / warps, 32 * warps, per_warp * warps, stream>>>(logits, correction, seq_of_token, chosen, share,
                                                                         counts, identity_share, num_tokens, outputs,
                                                                         real_experts, top, groups, keep, weight_scale,
                                                                         share_eps);
