@@ -467,6 +467,29 @@ def test_routed_experts_in_groups_with_identity_experts(dtype, experts, identity
     rows_close(got, want, dtype)
 
 
+@pytest.mark.parametrize("outputs, identity, top, groups, keep, tokens", [
+    (2048, 48, 9, 1024, 37, 11), (1500, 0, 5, 3, 2, 70), (96, 5, 8, 32, 8, 33), (33, 1, 33, 1, 1, 5), (64, 60, 2, 64, 2, 9)])
+def test_grouped_router_alone_at_many_outputs(outputs, identity, top, groups, keep, tokens):
+    """The routing kernel against the plain router: more outputs than a lane holds, more groups than lanes, every output chosen,
+    nearly all of them identity experts."""
+    from tinyserve_llm_b200.ops import get_ops
+    g = torch.Generator().manual_seed(outputs + top)
+    logits = torch.randn(tokens, outputs, generator=g) * 2.0
+    correction = torch.randn(outputs, generator=g) * 0.05 - 0.02
+    r = {"experts": outputs - identity, "identity": identity, "top": top, "scale": 1.7, "groups": {"count": groups, "keep": keep}}
+    want_chosen, want_share = plain.route(logits.double(), {"router": torch.eye(outputs, dtype=torch.float64),
+                                                            "correction": correction.double()}, r)
+    chosen, share, _, _, _, identity_share = get_ops().moe_route_grouped(
+        logits.cuda(), correction.cuda(), SimpleNamespace(), top, real_experts=outputs - identity, groups=groups, keep=keep,
+        weight_scale=1.7, share_eps=1e-20)
+    expected = torch.where(want_chosen < outputs - identity, want_chosen, torch.full_like(want_chosen, -1))
+    assert chosen.cpu().tolist() == expected.tolist()                      # in the order of the choice scores
+    torch.testing.assert_close(share.cpu().double(), want_share, rtol=2e-5, atol=1e-7)
+    if identity:
+        torch.testing.assert_close(identity_share.cpu().double(), (want_share * (want_chosen >= outputs - identity)).sum(-1),
+                                   rtol=2e-5, atol=1e-7)
+
+
 def test_grouped_router_choices_by_hand():
     """
     Scores over all outputs, choice by score + correction inside the kept groups, shares without the

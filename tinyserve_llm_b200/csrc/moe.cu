@@ -203,7 +203,7 @@ TS_API int ts_moe_route_grouped(const float* logits, const float* correction, co
     TS_REQUIRE(real_experts == outputs || identity_share, "moe_route: identity experts need a place for their shares");
     if (num_tokens <= 0) return 0;
     const size_t per_warp = (size_t)2 * (outputs + groups) * sizeof(float);           // at most 24 KB
-    const int warps = per_warp * 4 <= 48 * 1024 ? 4 : (per_warp * 2 <= 48 * 1024 ? 2 : 1);
+    const int warps = per_warp * 4 <= 48 * 1024 ? 4 : 2;
     moe_route_grouped_kernel<<<(num_tokens + warps - 1) / warps, 32 * warps, per_warp * warps, stream>>>(logits, correction, seq_of_token, chosen, share,
                                                                         counts, identity_share, num_tokens, outputs,
                                                                         real_experts, top, groups, keep, weight_scale,
