@@ -418,20 +418,26 @@ def test_embedding_with_scale_and_sinusoid(dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("p, q", [(0.3, -0.8), (-2.0, 1.5)])
-def test_dense_feed_forward_with_xielu(dtype, p, q):
+@pytest.mark.parametrize("width, ff, tokens", [(48, 72, 40), (64, 104, 5), (96, 40, 32)])
+def test_dense_feed_forward_with_xielu(dtype, p, q, width, ff, tokens):
+    """Many rows (the product, then the activation's own pass) and a few (the activation in the product's epilogue)."""
     from tinyserve_llm_b200.config.spec import PlainMLPSpec
     from tinyserve_llm_b200.parts.base import part_class
     from tinyserve_llm_b200.weights import random_tensors
-    width, ff = 48, 72
     spec = PlainMLPSpec(hidden_size=width, intermediate_size=ff, activation="xielu", param_name="act")
     cls = part_class("feed_forward", spec)
     tensors = dict(random_tensors(cls.declare(spec), 19, std=0.3))
     tensors["act"] = torch.tensor([p, q]).to(tensors["act"].dtype)
     part = cls(spec, {k: v.cuda() for k, v in tensors.items()}, _runtime(dtype))
     g = torch.Generator().manual_seed(2)
-    x = torch.randn(40, width, generator=g).to(dtype)
+    x = torch.randn(tokens, width, generator=g).to(dtype)
     got = part.forward(x.cuda(), SimpleNamespace()).cpu().double()
     rows_close(got, plain.dense_ff(x.double(), {k: v.double() for k, v in tensors.items()}), dtype)
+    # the activation gives the same numbers in the epilogue as in a pass of its own
+    ops = part.rt.ops
+    fused = ops.linear_unary(x.cuda(), part.up.weight, "xielu", *part.factors)
+    apart = ops.unary_activation(ops.linear(x.cuda(), part.up.weight), "xielu", *part.factors)
+    assert torch.equal(fused, apart)
 
 
 ROUTERS = [(7, 2, 2, (3, 2), 1.5, 50), (5, 0, 3, (1, 1), 0.7, 3), (6, 3, 1, (3, 1), 2.0, 50), (40, 8, 4, (8, 3), 1.0, 50),

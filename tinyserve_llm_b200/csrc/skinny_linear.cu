@@ -46,6 +46,8 @@ struct RopeArgs {
     int nh, nkv, hd, write_kv;
     int act;                     // gated epilogue: the activation (TS_ACT_*), with its constants
     float act_limit, act_alpha;
+    int unary;                   // store epilogue: 1 + TS_UNARY_* of an activation of one argument (0: none), a, b below
+    float unary_a, unary_b;
 };
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -277,6 +279,8 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
 #pragma unroll
             for (int w = 0; w < WARPS; ++w) v += partial[w][t][l][e];
             const int row = (l >> 2) + ((e >> 1) << 3), token = t * 8 + ((l & 3) << 1) + (e & 1);
+            // an activation of one argument reads the product as the separate kernel would: rounded to the output type
+            if (rope.unary) v = ts_unary_activation(rope.unary - 1, round_to<OUT>(v), rope.unary_a, rope.unary_b);
             if (row < rows_valid && token < M) store_out<OUT>(y + (long long)token * ldy + blockIdx.x * ROWS + row, v);
         }
     }
@@ -357,6 +361,25 @@ TS_API int ts_skinny_linear(const void* W, const void* x, void* y, int M, int N,
     if (out_dtype == TS_BF16) return dispatch_warps<EPI_STORE, __nv_bfloat16>(W, x, y, M, N, K, ldx, ldy, 0, stream);
     if (out_dtype == TS_F32) return dispatch_warps<EPI_STORE, float>(W, x, y, M, N, K, ldx, ldy, 0, stream);
     return ts_fail("skinny_linear: unknown output dtype code %d", out_dtype);
+}
+
+// y[M, N] = act(x . W^T) with an activation of one argument (TS_UNARY_* of common.cuh, its numbers a, b) in the epilogue.
+TS_API int ts_skinny_linear_unary(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy,
+                                  int kind, float a, float b, int out_dtype, cudaStream_t stream) {
+    TS_REQUIRE(M >= 0 && N > 0 && K > 0, "skinny_linear_unary: bad sizes M=%d N=%d K=%d", M, N, K);
+    TS_REQUIRE(M <= ts_skinny_linear_max_rows(), "skinny_linear_unary: %d rows of x; the kernel takes up to %d", M,
+               ts_skinny_linear_max_rows());
+    TS_REQUIRE(K % 32 == 0 && ldx % 8 == 0 && ((uintptr_t)W % 16 == 0) && ((uintptr_t)x % 16 == 0),
+               "skinny_linear_unary: K a multiple of 32 and 16-byte aligned operands are needed");
+    TS_REQUIRE(kind == TS_UNARY_RELU2 || kind == TS_UNARY_XIELU, "skinny_linear_unary: unknown activation %d", kind);
+    if (M == 0) return 0;
+    RopeArgs args{};
+    args.unary = kind + 1;
+    args.unary_a = a;
+    args.unary_b = b;
+    if (out_dtype == TS_BF16) return dispatch_warps<EPI_STORE, __nv_bfloat16>(W, x, y, M, N, K, ldx, ldy, 0, stream, args);
+    if (out_dtype == TS_F32) return dispatch_warps<EPI_STORE, float>(W, x, y, M, N, K, ldx, ldy, 0, stream, args);
+    return ts_fail("skinny_linear_unary: unknown output dtype %d", out_dtype);
 }
 
 // y[M, N/2] = act(x Wgate^T, x Wup^T) with another gated activation than SiLU in the epilogue (TS_ACT_* of common.cuh).

@@ -51,6 +51,7 @@ _SIGNATURES = {
     "ts_skinny_linear": ("int", "pppiiilliip"),
     "ts_skinny_qkv_rope_store": ("int", "pppiilpppiipipplliiiiiip"),
     "ts_skinny_linear_gated": ("int", "pppiiilliffp"),
+    "ts_skinny_linear_unary": ("int", "pppiiilliffip"),
     "ts_gemm_tcgen05_gated": ("int", "pppiiilliffpp"),
     "ts_stream_norm": ("int", "ppppppiifppifiippp"),
     "ts_linear_recurrence": ("int", "ppplllplppfffpipppiplpiiiipip"),
@@ -1118,6 +1119,25 @@ class Ops:
         """A few rows of bfloat16 x (a decode step): the engine's own weight-streaming kernel takes them."""
         return (x.dtype == torch.bfloat16 and 0 < x.shape[0] <= self.skinny_max_rows and x.shape[1] % 32 == 0
                 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+    def linear_unary(self, x: torch.Tensor, weight: torch.Tensor, kind: str, a: float = 0.0, b: float = 0.0) -> torch.Tensor:
+        """
+        act(x . weight^T) for the activations of `unary_activation`, [M, N]: a few rows of bfloat16 x on the
+        weight-streaming kernel with the activation in its epilogue (it reads the product rounded to bfloat16, as
+        the separate kernel does, so both ways give the same numbers); else the product and the activation kernel.
+        """
+        if kind not in self.UNARY_ACTIVATIONS:
+            raise KernelError(f"linear_unary: kind {kind!r} of {sorted(self.UNARY_ACTIVATIONS)}")
+        self._check(x, "x", tuple(_DTYPE_CODE), 2)
+        self._check(weight, "weight", x.dtype, 2)
+        if x.shape[1] != weight.shape[1]:
+            raise KernelError(f"linear_unary: x has {x.shape[1]} columns, the weight {weight.shape[1]}")
+        if not self._skinny(x, weight):
+            return self.unary_activation(self.linear(x, weight), kind, a, b)
+        out = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
+        self._call("ts_skinny_linear_unary", _ptr(weight), _ptr(x), _ptr(out), x.shape[0], weight.shape[0], x.shape[1],
+                   x.shape[1], weight.shape[0], self.UNARY_ACTIVATIONS[kind], float(a), float(b), _DTYPE_CODE[x.dtype], _stream())
+        return out
 
     def linear_gated(self, x: torch.Tensor, gate_up_weight: torch.Tensor, activation: str, limit: float = 0.0,
                      alpha: float = 1.0) -> torch.Tensor:

@@ -85,4 +85,5 @@ class PlainMLP(FeedForward):
             self.factors = (softplus(p), 0.5 + softplus(q))
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        return self.down(self.rt.ops.unary_activation(self.up(x), self.spec.activation, *self.factors))
+        # a few rows: the activation rides in the up product's epilogue; more: the library's product, then one pass
+        return self.down(self.rt.ops.linear_unary(x, self.up.weight, self.spec.activation, *self.factors))
