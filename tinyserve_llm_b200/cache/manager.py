@@ -45,10 +45,15 @@ class GroupLayout:
     window: int = 0                   # 0: all keys kept
     values: bool = True               # False: no value pool (mixers that keep one row per token)
     value_dim: int = 0                # head size of the values where it differs from head_dim (0: the same)
+    value_heads: int = 0              # heads of the value pool where they differ from num_kv_heads (0: the same)
 
     @property
     def value_head_dim(self) -> int:
         return self.value_dim or self.head_dim
+
+    @property
+    def num_value_heads(self) -> int:
+        return self.value_heads or self.num_kv_heads
 
 
 @dataclass(frozen=True)
@@ -79,20 +84,22 @@ def plan_layout(needs: Sequence[tuple[object | None, int]], page_tokens: int) ->
     """
     if page_tokens <= 0:
         raise ValueError(f"page size must be positive, got {page_tokens}")
-    by_geometry: dict[tuple[int, int, int, bool, int], list[int]] = {}
+    by_geometry: dict[tuple[int, int, int, bool, int, int], list[int]] = {}
     offsets, total = [], 0
     sizes = tuple(int(state) for _, state in needs)
     for e, (kv, state) in enumerate(needs):
         if kv is not None:
             value_dim = int(getattr(kv, "value_dim", 0) or 0)
+            value_heads = int(getattr(kv, "value_heads", 0) or 0)
             by_geometry.setdefault((kv.num_kv_heads, kv.head_dim, kv.window, bool(getattr(kv, "values", True)),
-                                    0 if value_dim == kv.head_dim else value_dim), []).append(e)
+                                    0 if value_dim == kv.head_dim else value_dim,
+                                    0 if value_heads == kv.num_kv_heads else value_heads), []).append(e)
         if state > 0:
             offsets.append(total)
             total += -(-state // 256) * 256         # slots of each entry start 256-byte aligned
         else:
             offsets.append(-1)
-    groups = tuple(GroupLayout(tuple(es), nkv, hd, w, vals, vd) for (nkv, hd, w, vals, vd), es in by_geometry.items())
+    groups = tuple(GroupLayout(tuple(es), nkv, hd, w, vals, vd, vh) for (nkv, hd, w, vals, vd, vh), es in by_geometry.items())
     return CacheLayout(page_tokens, groups, tuple(offsets), total, sizes)
 
 

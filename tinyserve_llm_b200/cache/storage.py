@@ -34,7 +34,7 @@ class EntryBinding:
     group: int = 0
     state: torch.Tensor | None = None            # uint8 [slots, bytes of this entry's state]
     state_slots: torch.Tensor | None = None      # int32 [sequences] on the device, set per step
-    v_page_stride: int = -1   # the value pool's geometry where its head size differs from the keys' (-1: the same)
+    v_page_stride: int = -1   # the value pool's geometry where its head size or head count differs from the keys' (-1: the same)
     v_entry_offset: int = -1
 
     def value_geometry(self) -> tuple[int, int]:
@@ -57,7 +57,7 @@ class DeviceCacheStorage:
         for group, pages in zip(layout.groups, counts):
             shape = (pages, len(group.entries), group.num_kv_heads, layout.page_tokens, group.head_dim)
             self.k_pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
-            v_shape = shape[:4] + (group.value_head_dim,)
+            v_shape = (pages, len(group.entries), group.num_value_heads, layout.page_tokens, group.value_head_dim)
             self.v_pools.append(torch.zeros(v_shape, dtype=dtype, device=self.device) if group.values else None)
         self.state = None
         if layout.state_bytes:
@@ -66,7 +66,8 @@ class DeviceCacheStorage:
     @staticmethod
     def bytes_per_page(layout: CacheLayout, dtype: torch.dtype) -> list[int]:
         """Keys and values of one page across the entries of each group."""
-        return [len(g.entries) * g.num_kv_heads * layout.page_tokens * (g.head_dim + (g.value_head_dim if g.values else 0))
+        return [len(g.entries) * layout.page_tokens * (g.num_kv_heads * g.head_dim +
+                                                       (g.num_value_heads * g.value_head_dim if g.values else 0))
                 * dtype.itemsize for g in layout.groups]
 
     def entry_binding(self, entry: int) -> EntryBinding | None:
@@ -80,8 +81,8 @@ class DeviceCacheStorage:
             per_entry = group.num_kv_heads * self.layout.page_tokens * group.head_dim
             binding = EntryBinding(self.k_pools[g], self.v_pools[g], per_entry * len(group.entries), per_entry * index,
                                    self.layout.page_tokens, self.num_pages[g], group=g)
-            if group.values and group.value_head_dim != group.head_dim:
-                per_entry_v = group.num_kv_heads * self.layout.page_tokens * group.value_head_dim
+            if group.values and (group.value_head_dim != group.head_dim or group.num_value_heads != group.num_kv_heads):
+                per_entry_v = group.num_value_heads * self.layout.page_tokens * group.value_head_dim
                 binding.v_page_stride, binding.v_entry_offset = per_entry_v * len(group.entries), per_entry_v * index
         offset = self.layout.state_offsets[entry] if entry < len(self.layout.state_offsets) else -1
         if offset >= 0:

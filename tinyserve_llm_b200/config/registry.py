@@ -14,6 +14,7 @@ from dataclasses import dataclass
 from typing import Any, Callable, Mapping
 
 from tinyserve_llm_b200.config.duduvik import DuduvikConfig, duduvik_model_spec
+from tinyserve_llm_b200.config.folavik import FolavikConfig, folavik_model_spec
 from tinyserve_llm_b200.config.llama import ConfigError, LlamaConfig, llama_model_spec
 from tinyserve_llm_b200.config.lugipel import LugipelConfig, lugipel_model_spec
 from tinyserve_llm_b200.config.nipizen import NipizenConfig, nipizen_model_spec
@@ -40,6 +41,7 @@ register_architecture(Architecture("LlamaForCausalLM", "llama", LlamaConfig.from
 register_architecture(Architecture("Duduvik", "duduvik", DuduvikConfig.from_dict, duduvik_model_spec))
 register_architecture(Architecture("Nipizen", "nipizen", NipizenConfig.from_dict, nipizen_model_spec))
 register_architecture(Architecture("Lugipel", "lugipel", LugipelConfig.from_dict, lugipel_model_spec))
+register_architecture(Architecture("Folavik", "folavik", FolavikConfig.from_dict, folavik_model_spec))
 
 
 def resolve_architecture(raw: Mapping[str, Any]) -> Architecture:

@@ -84,13 +84,16 @@ class InlineRotarySpec(PartSpec):
     """
     Rotate-half rotation over the first `dims` channels of a head, channel i paired with i + dims/2,
     angle = position * base^(-2i/dims), computed in float32 inside the kernels (no position table,
-    so no longest position).  `yarn` rescales the frequencies and magnifies cos and sin.
+    so no longest position).  `yarn` rescales the frequencies and magnifies cos and sin; `bands` rescales
+    them by wavelength (short waves kept, long ones divided by the factor, a blend in between); at most one
+    of the two.
     """
 
     kind: str = field(init=False, default="rotary_inline")
     dims: int = 0
     base: float = 10000.0
     yarn: YarnScaling | None = None
+    bands: Llama3Scaling | None = None
 
 
 @dataclass(frozen=True)
@@ -124,7 +127,9 @@ class LinearRecurrenceSpec(PartSpec):
 class LatentAttentionSpec(PartSpec):
     """
     Softmax attention whose per-head keys and values are up-projections of one cached latent per
-    token; queries go through a normed latent of their own; one rotated key part is shared by the heads.
+    token; queries go through a normed latent of their own (`q_rank` 0: they are a projection of the input,
+    tensor `q`); one rotated key part is shared by the heads (`rot_dim` 0: none, and no `position`);
+    `output_gate`: the concatenated heads are multiplied by sigmoid(W_g h) before the output projection.
     """
 
     kind: str = field(init=False, default="latent_attention")
@@ -139,6 +144,7 @@ class LatentAttentionSpec(PartSpec):
     window: int = 0                      # 0: every earlier key; w > 0: the last w keys, the query's own included
     norm_eps: float = 1e-6
     position: PartSpec | None = None
+    output_gate: bool = False
 
 
 @dataclass(frozen=True)
@@ -211,7 +217,9 @@ class GatedAttentionSpec(PartSpec):
     `distance_slope_exponent` c > 0 takes slope_h * (i - j) off the score of query i and key j,
     slope_h = 2^(-c (h + 1) / num_heads); `head_bias` adds the number `pb`[h] to every score of head h;
     `weights` "sigmoid" makes a visible key's weight sigmoid(score) without any normalisation over
-    the keys; `output_gate_scope` "head" gates with one number a head (`g` is [num_heads, hidden]).
+    the keys; `output_gate_scope` "head" gates with one number a head (`g` is [num_heads, hidden]);
+    `chunk` n > 0 lets query i see key j only if floor(i / n) = floor(j / n), positions counted from the
+    request's first token; `softcap` c > 0 turns the scaled product into c tanh(q . k * scale / c).
     """
 
     kind: str = field(init=False, default="gated_attention")
@@ -234,6 +242,36 @@ class GatedAttentionSpec(PartSpec):
     head_bias: bool = False
     weights: str = "softmax"             # "softmax" over the visible keys, or "sigmoid" of each score
     output_gate_scope: str = "channel"   # "channel": a gate a value channel; "head": one a head
+    chunk: int = 0                       # 0: no chunks
+    softcap: float = 0.0                 # 0: scores are not capped
+
+
+@dataclass(frozen=True)
+class DifferentialAttentionSpec(PartSpec):
+    """
+    Grouped-query attention whose heads each hold `maps` = 2 score maps over the same values: q has
+    num_heads * 2 * head_dim rows and k num_kv_heads * 2 * head_dim, head by head as [map 1 | map 2]; each map is
+    a softmax attention of its own (rotation, score scale, `softcap`, `window` and `chunk` as in
+    `GatedAttentionSpec`), and a head's output is
+        (a_1 - lambda a_2) / sqrt(mean((a_1 - lambda a_2)^2) + norm_eps) * (1 - difference)
+    over its value_dim channels (no weight), lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + difference, one number
+    for the layer from four tensors of head_dim elements.  `bias`: q, k and v have biases (name + ".b").
+    """
+
+    kind: str = field(init=False, default="differential_attention")
+    hidden_size: int = 0
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    head_dim: int = 0
+    value_dim: int = 0
+    scale: float = 0.0
+    window: int = 0
+    chunk: int = 0
+    softcap: float = 0.0
+    difference: float = 0.0
+    norm_eps: float = 1e-6
+    bias: bool = False
+    position: PartSpec | None = None
 
 
 @dataclass(frozen=True)
@@ -319,7 +357,8 @@ class GatedMLPSpec(PartSpec):
     hidden_size: int = 0
     intermediate_size: int = 0
     # "silu": silu(g) * u; "relu": relu(g) * u;
-    # "clamped_swish": g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit)
+    # "clamped_swish": g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit);
+    # "gelu_tanh": g/2 (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) u
     activation: str = "silu"
     limit: float = 0.0
     alpha: float = 1.0
@@ -421,6 +460,10 @@ class ModelSpec:
     extras: dict[str, Any] = field(default_factory=dict, compare=False)
     embedding_scale: float = 1.0               # multiplies the embedding rows as they start the stream (not the tied head)
     embedding_position: PartSpec | None = None  # a position vector added to the scaled embedding rows (`SinusoidSpec`)
+    embedding_norm: PartSpec | None = None     # a norm of the embedding rows before they start the stream (a stream norm's spec)
+    embedding_norm_prefix: str = ""            # where its tensors live
+    logit_scale: float = 1.0                   # multiplies the logits
+    logit_softcap: float = 0.0                 # c > 0: logits <- c tanh(logits / c), after the scale
 
     @property
     def num_cache_entries(self) -> int:

@@ -15,6 +15,11 @@
 //   score(i, j) = q_i . k_j * scale - slopes[h] * (i - j) + head_bias[h]      (each term optional)
 //   SIGMOID: the weight of a visible key is sigmoid(score), with no normalisation over the keys
 //   gate: head h's output is multiplied by sigmoid(gate[t, h]) (one logit a token and head)
+//   softcap c > 0: the scaled product becomes c tanh(q_i . k_j * scale / c) before the other terms
+//   chunk n > 0: a query also sees no key before floor(i / n) * n (positions count from the request's first token)
+//   out_f32: the output is written in float32 whatever the activation dtype
+//   value_heads g > 0: the value pool holds g heads (a divisor of nkv), head h reads value head h / (nh / g): several
+//     key heads, each with query heads of its own, over one set of values
 #include "common.cuh"
 
 struct AttentionExtras {
@@ -22,6 +27,10 @@ struct AttentionExtras {
     const float* head_bias;    // [nh] or null
     const void* gate;          // [tokens, nh] logits in the activation dtype, `gate_stride` elements a row, or null
     long long gate_stride;
+    float softcap;             // 0: none
+    int chunk;                 // 0: none
+    int value_heads;           // 0: as many as key heads
+    int out_f32;               // 1: `out` is float32 whatever the activation dtype
 };
 
 template <typename T>
@@ -81,9 +90,12 @@ paged_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* _
     const float slope = extras.slopes ? extras.slopes[h] : 0.f;
     const float bias = extras.head_bias ? extras.head_bias[h] : 0.f;
 
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (extras.chunk > 0) lo = max(lo, pos / extras.chunk * extras.chunk);
+    const int vh = extras.value_heads > 0 ? h / (nh / extras.value_heads) : kvh;
+    const float cap = extras.softcap, inv_cap = cap > 0.f ? 1.f / cap : 0.f;
     const long long head_off = geo.entry_offset + (long long)kvh * geo.page_tokens * hd;
-    const long long head_off_v = geo_v.entry_offset + (long long)kvh * geo.page_tokens * vd;
+    const long long head_off_v = geo_v.entry_offset + (long long)vh * geo.page_tokens * vd;
     const int* table = block_table + (long long)seq * table_width;
     for (int j = lo + lane; j <= pos; j += 32) {
         const int page = table[j / geo.page_tokens];
@@ -105,6 +117,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* _
 #pragma unroll 4
             for (int d = 0; d < hd; ++d) s = fmaf(q_smem[warp][d], to_float<T>(kp[d]), s);
         }
+        if (cap > 0.f) s = cap * tanhf(s * inv_cap);
         s = s - slope * (float)(pos - j) + bias;
         float p;
         if (SIGMOID) {
@@ -151,7 +164,10 @@ paged_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* _
     for (int d = 0; d < MAXHD; ++d) {
         if (d < vd) {
             const float total = warp_sum(o[d] * f);
-            if (lane == (d & 31)) o_ptr[d] = from_float<T>(total * inv);
+            if (lane == (d & 31)) {
+                if (extras.out_f32) reinterpret_cast<float*>(out)[((long long)t * nh + h) * vd + d] = total * inv;
+                else o_ptr[d] = from_float<T>(total * inv);
+            }
         }
     }
 }
@@ -189,8 +205,11 @@ TS_API int ts_paged_attention_scored(const void* q, long long q_stride, void* ou
                                      int table_width, const int* positions, const int* seq_of_token, int num_tokens,
                                      int nh, int nkv, int hd, int vd, float scale, int window, int dtype, int sigmoid,
                                      const float* slopes, const float* head_bias, const void* gate, long long gate_stride,
-                                     cudaStream_t stream) {
-    const AttentionExtras extras{slopes, head_bias, gate, gate_stride};
+                                     float softcap, int chunk, int value_heads, int out_f32, cudaStream_t stream) {
+    const AttentionExtras extras{slopes, head_bias, gate, gate_stride, softcap, chunk, value_heads, out_f32};
+    TS_REQUIRE(softcap >= 0.f && chunk >= 0 && value_heads >= 0, "paged_attention: bad softcap, chunk or value heads");
+    TS_REQUIRE(value_heads == 0 || (nkv % value_heads == 0 && nh % value_heads == 0),
+               "paged_attention: %d value heads do not divide %d key heads", value_heads, nkv);
     TS_REQUIRE(num_tokens >= 0 && nh > 0 && nkv > 0, "paged_attention: bad sizes");
     TS_REQUIRE(nh % nkv == 0, "paged_attention: %d query heads are not a multiple of %d kv heads", nh, nkv);
     TS_REQUIRE(hd > 0 && hd <= 256 && vd > 0 && vd <= 256,
@@ -225,7 +244,7 @@ TS_API int ts_paged_attention_split(const void* q, long long q_stride, void* out
     return ts_paged_attention_scored(q, q_stride, out, k_pool, v_pool, page_stride, entry_offset, v_page_stride,
                                      v_entry_offset, page_tokens, num_pages, block_table, table_width, positions,
                                      seq_of_token, num_tokens, nh, nkv, hd, vd, scale, window, dtype, 0, nullptr, nullptr,
-                                     nullptr, 0, stream);
+                                     nullptr, 0, 0.f, 0, 0, 0, stream);
 }
 
 // Queries, keys and values of one head size in the columns [q | k | v] of one projection's output.

@@ -45,12 +45,14 @@ __global__ void latent_prepare_kernel(const T* __restrict__ y, long long y_strid
     if (seq < 0) return;
     const T* row = y + (long long)t * y_stride;
     float acc = 0.f;
-    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) { const float x = to_float<T>(row[i]); acc += x * x; }
-    const float inv_q = 1.f / sqrtf(block_sum(acc, scratch) / (float)q_rank + eps);
-    for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
-        cq[(long long)t * q_rank + i] = from_float<T>(to_float<T>(row[i]) * inv_q * wq[i]);
+    if (q_rank > 0) {                                     // q_rank 0: the queries have no latent of their own
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) { const float x = to_float<T>(row[i]); acc += x * x; }
+        const float inv_q = 1.f / sqrtf(block_sum(acc, scratch) / (float)q_rank + eps);
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
+            cq[(long long)t * q_rank + i] = from_float<T>(to_float<T>(row[i]) * inv_q * wq[i]);
+        __syncthreads();
+    }
     if (!writes) return;
-    __syncthreads();
     acc = 0.f;
     for (int i = threadIdx.x; i < rank; i += blockDim.x) { const float x = to_float<T>(row[q_rank + i]); acc += x * x; }
     const float inv_c = 1.f / sqrtf(block_sum(acc, scratch) / (float)rank + eps);
@@ -76,7 +78,7 @@ TS_API int ts_latent_prepare(const void* y, long long y_stride, int q_rank, int 
                              const int* seq_of_token, void* cq, void* k_pool, long long page_stride, long long entry_offset,
                              int page_tokens, int num_pages, const int* block_table, int table_width, int writes,
                              int num_tokens, int dtype, cudaStream_t stream) {
-    TS_REQUIRE(q_rank > 0 && rank > 0 && rot >= 0 && rot % 2 == 0, "latent_prepare: bad sizes");
+    TS_REQUIRE(q_rank >= 0 && rank > 0 && rot >= 0 && rot % 2 == 0, "latent_prepare: bad sizes");
     TS_REQUIRE(page_tokens > 0 && table_width > 0, "latent_prepare: bad page geometry");
     if (num_tokens == 0) return 0;
     KVGeometry geo{page_stride, entry_offset, page_tokens, num_pages};

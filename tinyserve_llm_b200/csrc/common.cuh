@@ -53,8 +53,9 @@ template <typename T>
 __device__ __forceinline__ float round_to(float v) { return to_float<T>(from_float<T>(v)); }
 
 // Gated activations of feed-forward layers, act(gate, up):  0: silu(g) u;  1: relu(g) u;
-// 2: g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit).
-enum { TS_ACT_SILU = 0, TS_ACT_RELU = 1, TS_ACT_CLAMPED_SWISH = 2 };
+// 2: g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit);
+// 3: gelu(g) u in the tanh form, gelu(g) = g/2 (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).
+enum { TS_ACT_SILU = 0, TS_ACT_RELU = 1, TS_ACT_CLAMPED_SWISH = 2, TS_ACT_GELU_TANH = 3, TS_ACT_LAST = TS_ACT_GELU_TANH };
 
 __device__ __forceinline__ float ts_gated_activation(int kind, float g, float u, float limit, float alpha) {
     if (kind == TS_ACT_RELU) return fmaxf(g, 0.f) * u;
@@ -63,6 +64,8 @@ __device__ __forceinline__ float ts_gated_activation(int kind, float g, float u,
         u = fminf(fmaxf(u, -limit), limit);
         return g / (1.f + expf(-alpha * g)) * (u + 1.f);
     }
+    if (kind == TS_ACT_GELU_TANH)
+        return 0.5f * g * (1.f + tanhf(0.7978845608028654f * fmaf(0.044715f * g * g, g, g))) * u;
     return g / (1.f + expf(-g)) * u;
 }
 

@@ -603,7 +603,7 @@ TS_API int ts_gemm_tcgen05(const void* W, const void* x, void* y, int M, int N, 
 // The gated epilogue with another activation than SiLU (TS_ACT_* of common.cuh): y[M, N/2], bfloat16.
 TS_API int ts_gemm_tcgen05_gated(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy,
                                  int act, float limit, float alpha, int* error, cudaStream_t stream) {
-    TS_REQUIRE(act >= TS_ACT_SILU && act <= TS_ACT_CLAMPED_SWISH, "gemm_tcgen05: unknown activation %d", act);
+    TS_REQUIRE(act >= TS_ACT_SILU && act <= TS_ACT_LAST, "gemm_tcgen05: unknown activation %d", act);
     return gemm_tcgen05_launch(W, x, y, M, N, K, ldx, ldy, EPI_SWIGLU, TS_BF16, error, act, limit, alpha, stream);
 }
 

@@ -556,7 +556,7 @@ __global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __rest
 
 TS_API int ts_gated_activation(const void* gate_up, void* out, int num_tokens, int inter, int kind, float limit,
                                float alpha, int dtype, cudaStream_t stream) {
-    TS_REQUIRE(num_tokens >= 0 && inter > 0 && kind >= 0 && kind <= 2, "gated_activation: bad arguments");
+    TS_REQUIRE(num_tokens >= 0 && inter > 0 && kind >= 0 && kind <= TS_ACT_LAST, "gated_activation: bad arguments");
     if (num_tokens == 0) return 0;
     const long long total = (long long)num_tokens * inter;
     const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);

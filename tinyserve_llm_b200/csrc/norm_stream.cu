@@ -9,7 +9,8 @@
 // rows are normed into a compact output and the stream is not written: the final norm of the
 // wanted places), `ids` (the row is table[ids[r]] * scale and starts the stream: the embedding; with
 // `pos_freq` a sinusoidal position vector is added to it: entry 2i gets sin(position * pos_freq[i]),
-// entry 2i + 1 the cosine of the same angle, the angle a float32 product).
+// entry 2i + 1 the cosine of the same angle, the angle a float32 product; with `w_start` the gathered row is
+// itself normed with that weight, in the way the opening norm is, before it starts the stream: a norm on the embedding).
 // Statistics, weights, the sum and the stream are float32; the branch and `out` have the activation
 // dtype.  The weights are given as they multiply (an offset of the stored weight is added by the host).
 //
@@ -25,7 +26,8 @@ __global__ void stream_norm_kernel(const T* __restrict__ branch, const float* __
                                    const float* __restrict__ w_open, T* __restrict__ out,
                                    const int* __restrict__ rows, int width, float eps, const T* __restrict__ table,
                                    const int* __restrict__ ids, int table_rows, float scale, int write_stream,
-                                   int flags, const int* __restrict__ positions, const float* __restrict__ pos_freq) {
+                                   int flags, const int* __restrict__ positions, const float* __restrict__ pos_freq,
+                                   const float* __restrict__ w_start) {
     extern __shared__ float row[];                // width floats, then 32 of scratch
     float* scratch = row + width;
     const int r = blockIdx.x;
@@ -44,6 +46,20 @@ __global__ void stream_norm_kernel(const T* __restrict__ branch, const float* __
             }
         } else {
             for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = zeros ? 0.f : to_float<T>(tr[i]) * scale;
+        }
+        if (w_start) {                            // each thread reads back only the elements it wrote
+            float mean = 0.f;
+            if (flags & TS_NORM_CENTERED) {
+                float sum = 0.f;
+                for (int i = threadIdx.x; i < width; i += blockDim.x) sum += row[i];
+                mean = block_sum(sum, scratch) / (float)width;
+                __syncthreads();
+            }
+            float acc = 0.f;
+            for (int i = threadIdx.x; i < width; i += blockDim.x) acc += (row[i] - mean) * (row[i] - mean);
+            const float inv = 1.f / sqrtf(block_sum(acc, scratch) / (float)width + eps);
+            __syncthreads();                      // scratch is used again below
+            for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = (row[i] - mean) * inv * w_start[i];
         }
     } else if (branch && (flags & TS_NORM_PLAIN_ADD)) {
         const T* br = branch + (long long)src * width;
@@ -82,13 +98,14 @@ __global__ void stream_norm_kernel(const T* __restrict__ branch, const float* __
 TS_API int ts_stream_norm(const void* branch, const float* w_close, float* stream, const float* w_open, void* out,
                           const int* rows, int count, int width, float eps, const void* table, const int* ids,
                           int table_rows, float scale, int flags, int dtype, const int* positions, const float* pos_freq,
-                          cudaStream_t stream_handle) {
+                          const float* w_start, cudaStream_t stream_handle) {
     TS_REQUIRE(count >= 0 && width > 0, "stream_norm: bad sizes rows=%d width=%d", count, width);
     TS_REQUIRE(stream != nullptr, "stream_norm: no residual stream");
     TS_REQUIRE(!(branch && !w_close && !(flags & TS_NORM_PLAIN_ADD)), "stream_norm: a branch needs the weight of its closing norm");
     TS_REQUIRE(!(w_open && !out), "stream_norm: an opening norm needs an output");
     TS_REQUIRE(!(ids && (!table || branch)), "stream_norm: token ids need the table and exclude a branch");
     TS_REQUIRE(!(pos_freq && (!ids || !positions)), "stream_norm: a position vector needs token ids and positions");
+    TS_REQUIRE(!(w_start && !ids), "stream_norm: a norm on the embedding needs token ids");
     TS_REQUIRE(width <= 48 * 1024, "stream_norm: rows of %d elements are not supported", width);
     if (count == 0) return 0;
     // few rows (decoding) are bound by the chain of loads, not by their number: about four elements a thread and pass;
@@ -103,7 +120,7 @@ TS_API int ts_stream_norm(const void* branch, const float* w_close, float* strea
             cudaFuncSetAttribute(stream_norm_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         stream_norm_kernel<TYPE><<<count, threads, smem, stream_handle>>>(                                        \
             (const TYPE*)branch, w_close, stream, w_open, (TYPE*)out, rows, width, eps, (const TYPE*)table, ids,  \
-            table_rows, scale, write, flags, positions, pos_freq);                                                \
+            table_rows, scale, write, flags, positions, pos_freq, w_start);                                             \
     } while (0)
     if (dtype == TS_F32) TS_STREAM_NORM(float);
     else if (dtype == TS_BF16) TS_STREAM_NORM(__nv_bfloat16);

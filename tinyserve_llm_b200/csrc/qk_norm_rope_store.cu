@@ -9,7 +9,8 @@
 //   i + rot/2, angle = position * freq[i], cos and sin both multiplied by `magnitude`
 //   k and v go to the token's slot of the paged cache, q to a compact [tokens, heads * dim] tensor.
 //
-// Keys and values may differ in their head size, so the value pool has a geometry of its own.
+// Keys and values may differ in their head size and in their number of heads (`v_heads`: several key heads over
+// one value head), so the value pool has a geometry of its own.
 // One CTA a token; sums, angles and the rotation are float32, the stores round to the activation dtype.
 #include "common.cuh"
 
@@ -22,7 +23,7 @@ struct QKPrepareArgs {
     void* q_out;
     void* k_pool; void* v_pool; KVGeometry k_geo; KVGeometry v_geo;
     const int* block_table; int table_width; int writes;
-    int heads, kv_heads, dim, vdim;
+    int heads, kv_heads, dim, vdim, v_heads;
     int norm_per_head; float temp_coef; int temp_every;
 };
 
@@ -31,7 +32,7 @@ __global__ void qk_norm_rope_store_kernel(QKPrepareArgs p) {
     __shared__ float scratch[32];
     const int t = blockIdx.x;
     const int seq = p.seq_of_token[t];
-    const int nq = p.heads * p.dim, nk = p.kv_heads * p.dim, nv = p.kv_heads * p.vdim;
+    const int nq = p.heads * p.dim, nk = p.kv_heads * p.dim, nv = p.v_heads * p.vdim;
     T* q_out = (T*)p.q_out + (long long)t * nq;
     if (seq < 0) {                                    // a padding row
         for (int e = threadIdx.x; e < nq; e += blockDim.x) q_out[e] = from_float<T>(0.f);
@@ -134,7 +135,8 @@ TS_API int ts_qk_norm_rope_store(const void* y, long long y_stride, int q_off, i
                                  long long k_entry_offset, long long v_page_stride, long long v_entry_offset,
                                  int page_tokens, int num_pages, const int* block_table, int table_width, int writes,
                                  int num_tokens, int heads, int kv_heads, int dim, int vdim, int dtype,
-                                 int norm_per_head, float temp_coef, int temp_every, cudaStream_t stream) {
+                                 int norm_per_head, float temp_coef, int temp_every, int value_heads, cudaStream_t stream) {
+    TS_REQUIRE(value_heads >= 0, "qk_norm_rope_store: bad number of value heads");
     TS_REQUIRE(heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0 && num_tokens >= 0, "qk_norm_rope_store: bad sizes");
     TS_REQUIRE(rot >= 0 && rot <= dim && rot % 2 == 0, "qk_norm_rope_store: rotation over %d of %d channels", rot, dim);
     TS_REQUIRE(page_tokens > 0 && table_width > 0, "qk_norm_rope_store: bad page geometry");
@@ -143,7 +145,7 @@ TS_API int ts_qk_norm_rope_store(const void* y, long long y_stride, int q_off, i
                     rot > 0 ? freq : nullptr, rot, magnitude, positions, seq_of_token, q_out, k_pool, v_pool,
                     KVGeometry{k_page_stride, k_entry_offset, page_tokens, num_pages},
                     KVGeometry{v_page_stride, v_entry_offset, page_tokens, num_pages}, block_table, table_width, writes,
-                    heads, kv_heads, dim, vdim, norm_per_head, temp_coef, temp_every};
+                    heads, kv_heads, dim, vdim, value_heads > 0 ? value_heads : kv_heads, norm_per_head, temp_coef, temp_every};
     const size_t smem = norm_per_head ? (size_t)(heads + kv_heads) * sizeof(float) : 0;
     TS_REQUIRE(smem <= 32 * 1024, "qk_norm_rope_store: %d heads are not supported", heads + kv_heads);
     // many tokens: small CTAs, many of them on an SM (a CTA's life is a chain of loads and two sums); few tokens: wide ones

@@ -390,7 +390,7 @@ TS_API int ts_skinny_linear_gated(const void* W, const void* x, void* y, int M, 
                ts_skinny_linear_max_rows());
     TS_REQUIRE(K % 32 == 0 && ldx % 8 == 0 && ((uintptr_t)W % 16 == 0) && ((uintptr_t)x % 16 == 0),
                "skinny_linear_gated: K a multiple of 32 and 16-byte aligned operands are needed");
-    TS_REQUIRE(act >= TS_ACT_SILU && act <= TS_ACT_CLAMPED_SWISH, "skinny_linear_gated: unknown activation %d", act);
+    TS_REQUIRE(act >= TS_ACT_SILU && act <= TS_ACT_LAST, "skinny_linear_gated: unknown activation %d", act);
     if (M == 0) return 0;
     RopeArgs args{};
     args.act = act;

@@ -53,7 +53,7 @@ _SIGNATURES = {
     "ts_skinny_linear_gated": ("int", "pppiiilliffp"),
     "ts_skinny_linear_unary": ("int", "pppiiilliffip"),
     "ts_gemm_tcgen05_gated": ("int", "pppiiilliffpp"),
-    "ts_stream_norm": ("int", "ppppppiifppifiippp"),
+    "ts_stream_norm": ("int", "ppppppiifppifiipppp"),
     "ts_linear_recurrence": ("int", "ppplllplppfffpipppiplpiiiipip"),
     "ts_head_norm_gate": ("int", "piplpippliiififip"),
     "ts_latent_prepare": ("int", "pliiippfppppplliipiiiip"),
@@ -65,12 +65,12 @@ _SIGNATURES = {
     "ts_moe_linear": ("int", "plpipipiipiiiffpiip"),
     "ts_moe_combine": ("int", "pppppiiiippp"),
     "ts_moe_route_grouped": ("int", "pppppppiiiiiiffp"),
-    "ts_paged_attention_scored": ("int", "plpppllllii" "pippiiiiifiiipppl" "p"),
+    "ts_paged_attention_scored": ("int", "plpppllllii" "pippiiiiifiiipppl" "fiii" "p"),
     "ts_mingru_scan": ("int", "pliiiippppiplpiiiip"),
     "ts_unary_activation_rows": ("int", "ppliffip"),
     "ts_gated_activation": ("int", "ppiiiffip"),
     "ts_sgemm_nt_batched": ("int", "pppiiilllilllp"),
-    "ts_qk_norm_rope_store": ("int", "pliiipppppfpifpppppllllii" "piiiiiiiiifip"),
+    "ts_qk_norm_rope_store": ("int", "pliiipppppfpifpppppllllii" "piiiiiiiiifiip"),
     "ts_sigmoid_gate": ("int", "plplpliifip"),
     "ts_paged_attention_split": ("int", "plpppllllii" "pippiiiiifiip"),
     "ts_short_conv_silu": ("int", "plppppiplpiiiip"),
@@ -78,6 +78,8 @@ _SIGNATURES = {
     "ts_delta_prepare": ("int", "pplppppl" "ppiiiiffip"),
     "ts_mlstm_prepare": ("int", "ppllpplppffppiplpppiiiip"),
     "ts_row_scaled_activation": ("int", "ppppiiiip"),
+    "ts_difference_head_norm": ("int", "plipl" "piiii" "fffip"),
+    "ts_scale_tanh_cap": ("int", "plffp"),
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "f": ctypes.c_float}
 _RETURNS = {"int": ctypes.c_int, "long long": ctypes.c_longlong, "void": None, "const char*": ctypes.c_char_p}
@@ -246,6 +248,12 @@ class Ops:
         for kernel, (returns, arguments) in kernels.items():
             register_kernel(kernel, returns, arguments)
             self._bind(kernel, lib)
+
+    @staticmethod
+    def _check_rows(t: torch.Tensor, name: str) -> None:
+        """[rows, columns] of an activation dtype on the device whose rows may be stretches of wider rows."""
+        if not t.is_cuda or t.dtype not in _DTYPE_CODE or t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+            raise KernelError(f"{name} must be a [rows, columns] stretch of an activation dtype on the device")
 
     @staticmethod
     def _check(t: torch.Tensor, name: str, dtype: torch.dtype | tuple | None = None, dims: int | None = None) -> None:
@@ -431,19 +439,22 @@ class Ops:
                     w_open: torch.Tensor | None, eps: float, dtype: torch.dtype, rows: torch.Tensor | None = None,
                     table: torch.Tensor | None = None, ids: torch.Tensor | None = None, scale: float = 1.0,
                     centered: bool = False, plain_add: bool = False, positions: torch.Tensor | None = None,
-                    position_frequencies: torch.Tensor | None = None) -> torch.Tensor | None:
+                    position_frequencies: torch.Tensor | None = None, w_start: torch.Tensor | None = None) -> torch.Tensor | None:
         """
         stream (float32, in place) += closing norm of `branch` (if given; with `plain_add` the branch as
         it is); returns the opening norm of the sum in `dtype` (if `w_open` is given; with `centered` a
         layer norm without bias instead of an RMS norm).  With `rows` only those rows are normed, into a
         compact output, and the stream is left as it is.  With `table` and `ids` the rows
         table[ids] * scale start the stream instead, plus, with `positions` and `position_frequencies` (float32
-        [ceil(width / 2)]), the vector whose entry 2i is sin(position * frequency i) and entry 2i + 1 its cosine.
-        Weights are float32 and multiply as given.
+        [ceil(width / 2)]), the vector whose entry 2i is sin(position * frequency i) and entry 2i + 1 its cosine;
+        with `w_start` the gathered rows are normed with that weight (as the opening norm norms: RMS, or centered)
+        before they start the stream.  Weights are float32 and multiply as given.
         """
         self._check(stream, "residual stream", torch.float32, 2)
         width = stream.shape[1]
-        for w, name in ((w_close, "closing weight"), (w_open, "opening weight")):
+        if w_start is not None and ids is None:
+            raise KernelError("stream_norm: a norm on the embedding rows needs token ids")
+        for w, name in ((w_close, "closing weight"), (w_open, "opening weight"), (w_start, "embedding norm weight")):
             if w is not None:
                 self._check(w, name, torch.float32, 1)
                 if w.shape[0] != width:
@@ -472,7 +483,8 @@ class Ops:
         self._call("ts_stream_norm", _ptr(branch), _ptr(w_close), _ptr(stream), _ptr(w_open), _ptr(out), _ptr(rows), count,
                    width, eps, _ptr(table), _ptr(ids), table.shape[0] if table is not None else 0, scale,
                    (1 if centered else 0) | (2 if plain_add else 0), _DTYPE_CODE[dtype],
-                   _ptr(positions) if position_frequencies is not None else 0, _ptr(position_frequencies), _stream())
+                   _ptr(positions) if position_frequencies is not None else 0, _ptr(position_frequencies), _ptr(w_start),
+                   _stream())
         return out
 
     # ------------------------------------------------------------------ linear recurrences
@@ -543,13 +555,14 @@ class Ops:
     # ------------------------------------------------------------------ attention with normed queries and keys, gated recurrences
     def qk_norm_rope_store(self, y: torch.Tensor, offsets: tuple[int, int, int], biases, weights, eps: float, position,
                            ctx, binding, heads: int, kv_heads: int, dim: int, vdim: int, *, norm_per_head: bool = False,
-                           q_temperature: tuple[float, int] | None = None) -> torch.Tensor:
+                           q_temperature: tuple[float, int] | None = None, value_heads: int = 0) -> torch.Tensor:
         """
         From the projection's output y (q, k, v at the column `offsets`): biases added (float32 tensors or
         None), q and k RMS-normed over the whole projection with `weights` (q's, k's; or None; with
         `norm_per_head` every head by itself, the weights [dim]), rotated by `position` (frequencies, dims,
         magnitude), q multiplied by 1 + coef * ln(floor((position + 1) / every) + 1) for `q_temperature`
-        (coef, every), k and v stored into the token's cache slot.  Returns q [T, heads * dim].
+        (coef, every), k and v stored into the token's cache slot.  `value_heads` (0: as many as key heads): v
+        holds that many heads of vdim channels.  Returns q [T, heads * dim].
         """
         if y.dtype not in _DTYPE_CODE or y.dim() != 2 or y.stride(1) != 1:
             raise KernelError("qk_norm_rope_store: y must be a [T, columns] stretch of an activation dtype")
@@ -572,12 +585,14 @@ class Ops:
                    _ptr(ctx.seq_of_token), _ptr(q), _ptr(binding.k_pool), _ptr(binding.v_pool), binding.page_stride,
                    binding.entry_offset, v_page_stride, v_entry_offset, binding.page_tokens, binding.num_pages,
                    _ptr(binding.block_table), binding.table_width, 1 if binding.writes else 0, T, heads, kv_heads, dim,
-                   vdim, _DTYPE_CODE[y.dtype], 1 if norm_per_head else 0, float(coef), int(every), _stream())
+                   vdim, _DTYPE_CODE[y.dtype], 1 if norm_per_head else 0, float(coef), int(every), int(value_heads), _stream())
         return q
 
     def paged_attention_split(self, q: torch.Tensor, ctx, binding, nh: int, nkv: int, hd: int, vd: int, scale: float,
                               window: int, *, weights: str = "softmax", slopes: torch.Tensor | None = None,
-                              head_bias: torch.Tensor | None = None, head_gate: torch.Tensor | None = None) -> torch.Tensor:
+                              head_bias: torch.Tensor | None = None, head_gate: torch.Tensor | None = None,
+                              softcap: float = 0.0, chunk: int = 0, value_heads: int = 0,
+                              out_dtype: torch.dtype | None = None) -> torch.Tensor:
         """
         [T, nh * vd]: causal attention of q [T, nh * hd] over the entry's cached keys (head size hd) and
         values (head size vd).  Equal head sizes of 64 or 128 in bfloat16 run on the tensor-core kernels
@@ -586,16 +601,25 @@ class Ops:
         Options: `slopes` (float32 [nh]) takes slopes[h] * (i - j) off the score of query i and key j,
         `head_bias` (float32 [nh]) is added to every score of its head, `weights` "sigmoid" makes a visible
         key's weight sigmoid(score) with no normalisation, `head_gate` ([T, nh] logits, a column stretch of
-        the activation dtype) multiplies head h's output by sigmoid(head_gate[t, h]).
+        the activation dtype) multiplies head h's output by sigmoid(head_gate[t, h]); `softcap` c > 0 turns the
+        scaled product into c tanh(. / c); `chunk` n > 0 hides every key before floor(i / n) * n from query i;
+        `value_heads` g > 0: the value pool holds g heads and head h reads value head h / (nh / g); `out_dtype`
+        float32 keeps the output unrounded.
         """
         self._check(q, "q", tuple(_DTYPE_CODE), 2)
         if q.shape[1] != nh * hd:
             raise KernelError(f"paged_attention_split: q has {q.shape[1]} columns, expected {nh * hd}")
         if weights not in ("softmax", "sigmoid"):
             raise KernelError(f"paged_attention_split: weights {weights!r}")
-        if weights != "softmax" or slopes is not None or head_bias is not None or head_gate is not None:
+        if softcap < 0 or chunk < 0 or value_heads < 0 or (value_heads and (nkv % value_heads or nh % value_heads)):
+            raise KernelError(f"paged_attention_split: softcap {softcap}, chunk {chunk}, {value_heads} value heads for {nkv} key heads")
+        if out_dtype not in (None, q.dtype, torch.float32):
+            raise KernelError(f"paged_attention_split: output dtype {out_dtype}")
+        out_f32 = out_dtype == torch.float32 and q.dtype != torch.float32
+        if (weights != "softmax" or slopes is not None or head_bias is not None or head_gate is not None or softcap > 0
+                or chunk > 0 or value_heads > 0 or out_f32):
             return self._paged_attention_scored(q, ctx, binding, nh, nkv, hd, vd, scale, window, weights, slopes, head_bias,
-                                                head_gate)
+                                                head_gate, softcap, chunk, value_heads, out_f32)
         if (hd == vd and q.dtype == torch.bfloat16 and getattr(ctx, "cu_q", None) is not None
                 and self.lib.ts_attention_bf16_supported(hd, binding.page_tokens, nh, nkv)):
             # the tensor-core kernels read q from the columns of a [q | k | v] row: q alone is such a row's first part
@@ -611,7 +635,7 @@ class Ops:
         return out
 
     def _paged_attention_scored(self, q, ctx, binding, nh, nkv, hd, vd, scale, window, weights, slopes, head_bias,
-                                head_gate) -> torch.Tensor:
+                                head_gate, softcap=0.0, chunk=0, value_heads=0, out_f32=False) -> torch.Tensor:
         for t, name in ((slopes, "slopes"), (head_bias, "head bias")):
             if t is not None:
                 self._check(t, name, torch.float32, 1)
@@ -620,8 +644,9 @@ class Ops:
         if head_gate is not None and (head_gate.dtype != q.dtype or head_gate.dim() != 2 or head_gate.stride(1) != 1
                                       or tuple(head_gate.shape) != (q.shape[0], nh)):
             raise KernelError("paged_attention_split: the head gate must be a [T, heads] stretch of the activation dtype")
-        out = torch.empty((q.shape[0], nh * vd), dtype=q.dtype, device=q.device)
-        if (weights == "sigmoid" and hd == vd and q.dtype == torch.bfloat16 and getattr(ctx, "cu_q", None) is not None
+        out = torch.empty((q.shape[0], nh * vd), dtype=torch.float32 if out_f32 else q.dtype, device=q.device)
+        plain = softcap == 0 and chunk == 0 and value_heads == 0 and not out_f32
+        if (plain and weights == "sigmoid" and hd == vd and q.dtype == torch.bfloat16 and getattr(ctx, "cu_q", None) is not None
                 and q.stride(0) % 8 == 0 and self.lib.ts_attention_bf16_supported(hd, binding.page_tokens, nh, nkv)):
             # the tensor-core kernels: tiles of a prompt's portion, split keys for requests that feed one token
             num_seqs = ctx.ctx_lens.shape[0]
@@ -665,8 +690,31 @@ class Ops:
                    binding.num_pages, _ptr(binding.block_table), binding.table_width, _ptr(ctx.positions),
                    _ptr(ctx.seq_of_token), q.shape[0], nh, nkv, hd, vd, scale, window, _DTYPE_CODE[q.dtype],
                    1 if weights == "sigmoid" else 0, _ptr(slopes), _ptr(head_bias), _ptr(head_gate),
-                   head_gate.stride(0) if head_gate is not None else 0, _stream())
+                   head_gate.stride(0) if head_gate is not None else 0, float(softcap), int(chunk), int(value_heads),
+                   1 if out_f32 else 0, _stream())
         return out
+
+    def difference_head_norm(self, maps: torch.Tensor, ctx, heads: int, kv_heads: int, vdim: int, weight: float, eps: float,
+                             out_scale: float, dtype: torch.dtype) -> torch.Tensor:
+        """
+        Differential attention's last step.  maps [T, 2 * heads * vdim] (float32 or `dtype`) holds per token the two
+        maps' outputs in the order [key/value group][map][head in group][vdim]; returns [T, heads * vdim] in `dtype`:
+        per head (a_1 - weight * a_2) / sqrt(mean(.^2) + eps) * out_scale, heads in their own order.
+        """
+        self._check(maps, "maps", (torch.float32, dtype), 2)
+        if maps.shape[1] != 2 * heads * vdim or heads % kv_heads:
+            raise KernelError(f"difference_head_norm: rows of {maps.shape[1]} for {heads} heads of {vdim} over {kv_heads} groups")
+        out = torch.empty((maps.shape[0], heads * vdim), dtype=dtype, device=maps.device)
+        self._call("ts_difference_head_norm", _ptr(maps), maps.stride(0), 1 if maps.dtype == torch.float32 else 0, _ptr(out),
+                   out.stride(0), _ptr(ctx.seq_of_token), maps.shape[0], heads, kv_heads, vdim, float(weight), float(eps),
+                   float(out_scale), _DTYPE_CODE[dtype], _stream())
+        return out
+
+    def scale_tanh_cap(self, x: torch.Tensor, scale: float, cap: float) -> torch.Tensor:
+        """x (float32, in place) <- cap * tanh(x * scale / cap), or x * scale where cap is 0."""
+        self._check(x, "x", torch.float32)
+        self._call("ts_scale_tanh_cap", _ptr(x), x.numel(), float(scale), float(cap), _stream())
+        return x
 
     def mingru_scan(self, y: torch.Tensor, offsets: tuple[int, int, int], z_bias: torch.Tensor | None,
                     x_bias: torch.Tensor | None, ctx, binding, width: int, dtype: torch.dtype) -> torch.Tensor:
@@ -828,10 +876,12 @@ class Ops:
     def latent_prepare(self, y: torch.Tensor, ctx, binding, q_rank: int, rank: int, rot: int, q_weight: torch.Tensor,
                        kv_weight: torch.Tensor, eps: float, freq: torch.Tensor) -> torch.Tensor:
         """
-        y [T, q_rank + rank + rot] (the down projections' output): returns the normed query latent [T, q_rank]
-        and stores [norm(c) | rotated k_rot] into each token's slot of the cache entry.
+        y [T, q_rank + rank + rot] (the down projections' output, or a column stretch of it): returns the normed
+        query latent [T, q_rank] and stores [norm(c) | rotated k_rot] into each token's slot of the cache entry.
+        q_rank 0 (queries without a latent) and rot 0 (no rotated part, `freq` None) are allowed.
         """
-        self._check(y, "y", tuple(_DTYPE_CODE), 2)
+        if y.dtype not in _DTYPE_CODE or y.dim() != 2 or y.stride(1) != 1 or not y.is_cuda:
+            raise KernelError("latent_prepare: y must be a [T, columns] stretch of an activation dtype on the device")
         if y.shape[1] != q_rank + rank + rot:
             raise KernelError(f"latent_prepare: rows of {y.shape[1]} columns, expected {q_rank + rank + rot}")
         if binding.k_pool.dtype != y.dtype:
@@ -849,9 +899,9 @@ class Ops:
         """
         [T, heads, N]: head h's first k channels of x [T, heads * head_width] times w[h]^T, w [heads, N, k].
         float32: the engine's FFMA kernel, one product per head in one launch; bfloat16: the library's
-        batched product.  The result may be a strided view.
+        batched product.  x may be a column stretch of wider rows; the result may be a strided view.
         """
-        self._check(x, "x", tuple(_DTYPE_CODE), 2)
+        self._check_rows(x, "x")
         self._check(w, "w", x.dtype, 3)
         T, N = x.shape[0], w.shape[1]
         if x.shape[1] != heads * head_width or w.shape[0] != heads or w.shape[2] != k or k > head_width:
@@ -875,9 +925,10 @@ class Ops:
         [T, heads, rank] in q's dtype: per head the softmax-weighted sum of the cached latents, scores
         (q_lat . c + rotated q_rot . k_rot) * scale over the keys the window leaves visible.  q_lat is
         float32 [T, heads, rank] (any token and head strides); the rotated part of the query is read from
-        q [T, heads * q_head_width] at `q_rot_offset` inside each head and rotated here.
+        q [T, heads * q_head_width] (rows may be stretches of wider ones) at `q_rot_offset` inside each head and
+        rotated here; `rot` 0: there is no such part and `freq` may be None.
         """
-        self._check(q, "q", tuple(_DTYPE_CODE), 2)
+        self._check_rows(q, "q")
         if q_lat.dtype != torch.float32 or q_lat.stride(2) != 1 or tuple(q_lat.shape) != (q.shape[0], heads, rank):
             raise KernelError("latent_attention: q_lat must be float32 [T, heads, rank] with unit channel stride")
         if binding.k_pool.dtype != q.dtype:
@@ -908,7 +959,7 @@ class Ops:
         return out
 
     # ------------------------------------------------------------------ gated activations, routed experts
-    GATED_ACTIVATIONS = {"silu": 0, "relu": 1, "clamped_swish": 2}
+    GATED_ACTIVATIONS = {"silu": 0, "relu": 1, "clamped_swish": 2, "gelu_tanh": 3}
 
     def gated_activation(self, gate_up: torch.Tensor, kind: str, limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
         """[T, I] from [T, 2 I] = [gate | up]: silu(g) u, relu(g) u, or the clamped swish g' sigmoid(alpha g') (u' + 1)."""

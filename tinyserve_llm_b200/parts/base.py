@@ -35,6 +35,7 @@ class KVNeed:
     window: int = 0           # 0: all keys are kept; w > 0: only the last w
     values: bool = True       # False: the mixer keeps one row per token and head (no value pool)
     value_dim: int = 0        # head size of the values where it differs from the keys' (0: the same)
+    value_heads: int = 0      # heads of the value pool where they differ from the keys' (0: the same)
 
 
 @dataclass

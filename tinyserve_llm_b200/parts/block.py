@@ -133,6 +133,7 @@ class PreNormStreamBlock(PreNormBlock):
     takes_token_ids = True
     takes_embedding_scale = True
     takes_embedding_position = True
+    takes_embedding_norm = True
 
     @staticmethod
     def _members(spec: BlockSpec):
@@ -151,12 +152,15 @@ class PreNormStreamBlock(PreNormBlock):
             self.feed_forward_norm, self.feed_forward = built[2:]
 
     def forward(self, x, residual: torch.Tensor | None, ctx, binding, embedding: torch.Tensor | None = None,
-                embedding_scale: float = 1.0, embedding_position=None):
-        """`embedding_position`: a position part whose vector is added to the scaled embedding rows."""
+                embedding_scale: float = 1.0, embedding_position=None, embedding_norm=None):
+        """
+        `embedding_position`: a position part whose vector is added to the scaled embedding rows;
+        `embedding_norm`: a stream norm the rows pass before they start the stream.
+        """
         from tinyserve_llm_b200.parts.norm import PendingBranch
         if embedding is not None:
             h, residual = self.mixer_norm.forward_embedded(embedding, x, embedding_scale, positions=ctx.positions,
-                                                           position=embedding_position)
+                                                           position=embedding_position, start_norm=embedding_norm)
         else:
             h, residual = self.mixer_norm.forward(x, residual)
         branch = PendingBranch(self.mixer.forward(h, ctx, binding), None)

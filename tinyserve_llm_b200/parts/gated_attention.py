@@ -12,8 +12,10 @@ Options a design may switch on (`GatedAttentionSpec`): a norm of q and of k head
 weight shared by the heads; a query temperature q <- q (1 + c ln(floor((p + 1) / n) + 1)) at position
 p; a distance penalty slope_h (i - j) taken off the score with slope_h = 2^(-c (h + 1) / heads); a
 number per head added to every score; sigmoid weights instead of a softmax (a visible key's weight is
-sigmoid(score), nothing is normalised over the keys); an output gate of one number a head.  With any
-of the last four the attention runs on the kernels that carry them (`paged_attention_split`'s options).
+sigmoid(score), nothing is normalised over the keys); an output gate of one number a head; chunks of n
+positions, counted from the request's first token, outside of which a query sees nothing (the cache keeps
+the last n keys, as for a window of n); scores capped as c tanh(score / c).  With any of the last six the
+attention runs on the kernels that carry them (`paged_attention_split`'s options).
 
 Keys (rotated) and values live in the paged cache; one kernel norms, rotates and stores, one attends
 (the tensor-core kernels where keys and values share a head size they take, the generic one else),
@@ -33,6 +35,11 @@ from tinyserve_llm_b200.parts.linear import Linear, fuse_rows
 MAX_HEAD_DIM = 256      # csrc/attention_generic.cu
 
 
+def kept_keys(window: int, chunk: int) -> int:
+    """How many of the latest keys the cache has to keep for a mask of a window, of chunks, or both (0: all)."""
+    return min(window, chunk) if window > 0 and chunk > 0 else max(window, chunk)
+
+
 @register_part("mixer", "gated_attention")
 class GatedAttention(Mixer):
     graph_safe = True
@@ -48,8 +55,8 @@ class GatedAttention(Mixer):
             raise NotImplementedError(f"attention: norm scope {spec.qk_norm_scope!r}, gate scope {spec.output_gate_scope!r}")
         if spec.weights not in ("softmax", "sigmoid"):
             raise NotImplementedError(f"attention: weights {spec.weights!r}; have softmax and sigmoid")
-        if spec.q_temperature_every < 0 or spec.distance_slope_exponent < 0 or spec.window < 0:
-            raise ValueError("attention: q_temperature_every, distance_slope_exponent and window must not be negative")
+        if spec.q_temperature_every < 0 or spec.distance_slope_exponent < 0 or spec.window < 0 or spec.chunk < 0 or spec.softcap < 0:
+            raise ValueError("attention: q_temperature_every, distance_slope_exponent, window, chunk and softcap must not be negative")
 
     @classmethod
     def declare(cls, spec: GatedAttentionSpec) -> dict[str, TensorDecl]:
@@ -99,7 +106,7 @@ class GatedAttention(Mixer):
 
     def kv_need(self) -> KVNeed:
         s = self.spec
-        return KVNeed(s.num_kv_heads, s.head_dim, s.window, True, 0 if s.value_dim == s.head_dim else s.value_dim)
+        return KVNeed(s.num_kv_heads, s.head_dim, kept_keys(s.window, s.chunk), True, 0 if s.value_dim == s.head_dim else s.value_dim)
 
     def inner(self, y: torch.Tensor, x: torch.Tensor, ctx, binding, scale: float = 1.0,
               out: torch.Tensor | None = None) -> torch.Tensor:
@@ -113,7 +120,7 @@ class GatedAttention(Mixer):
         per_head_gate = s.output_gate and s.output_gate_scope == "head"
         o = ops.paged_attention_split(q, ctx, binding, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, s.scale, s.window,
                                       weights=s.weights, slopes=self.slopes, head_bias=self.head_bias,
-                                      head_gate=gate if per_head_gate else None)
+                                      head_gate=gate if per_head_gate else None, softcap=s.softcap, chunk=s.chunk)
         if per_head_gate:                               # the gate went into the attention kernel's last step
             if scale != 1.0:
                 o = o * scale

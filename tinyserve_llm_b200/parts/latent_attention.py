@@ -12,7 +12,12 @@ works on cache rows [c | k_rot] directly: keys and values of a head are never ma
 as in decoding.  The cache entry is one "kv head" of kv_rank + rot_dim channels without a value pool;
 a window makes it a layer group of its own whose pages are given back as the window passes.
 
-Tensors (local names): dq, dq.norm, uq, dkv, dkv.norm, uk, uv, o.
+Options of the description: `q_rank` 0 makes the queries a projection of the input, q = W_q h, without a
+latent and a norm of their own; `rot_dim` 0 leaves out the rotated part (attention without positions: the
+cache row is c alone and no position part is built); `output_gate` multiplies the concatenated heads by
+sigmoid(W_g h), read from the same input as the other projections, before W_o.
+
+Tensors (local names): dq, dq.norm, uq (or q), dkv, dkv.norm, uk, uv, o, and g with an output gate.
 """
 
 from __future__ import annotations
@@ -34,37 +39,52 @@ class LatentAttention(Mixer):
     def validate(cls, spec: LatentAttentionSpec) -> None:
         if spec.kv_rank > MAX_KV_RANK:
             raise ValueError(f"kv_rank={spec.kv_rank} is not supported: the latent attention kernel takes up to {MAX_KV_RANK}")
-        if spec.rot_dim % 2:
-            raise ValueError(f"rot_dim={spec.rot_dim} must be even")
+        if spec.rot_dim % 2 or spec.rot_dim < 0 or spec.q_rank < 0:
+            raise ValueError(f"rot_dim={spec.rot_dim} must be even and q_rank={spec.q_rank} not negative")
+        if (spec.rot_dim > 0) != (spec.position is not None):
+            raise ValueError("latent attention: a rotated key part and a position part come together")
 
     @classmethod
     def declare(cls, spec: LatentAttentionSpec) -> dict[str, TensorDecl]:
         cls.validate(spec)
         H, D, R, V = spec.num_heads, spec.head_dim, spec.rot_dim, spec.value_dim
-        return {
-            "dq": TensorDecl((spec.q_rank, spec.hidden_size)), "dq.norm": TensorDecl((spec.q_rank,), init="unit"),
-            "uq": TensorDecl((H * (D + R), spec.q_rank)),
+        out = {
             "dkv": TensorDecl((spec.kv_rank + R, spec.hidden_size)), "dkv.norm": TensorDecl((spec.kv_rank,), init="unit"),
             "uk": TensorDecl((H * D, spec.kv_rank)), "uv": TensorDecl((H * V, spec.kv_rank)),
             "o": TensorDecl((spec.hidden_size, H * V)),
         }
+        if spec.q_rank > 0:
+            out.update({"dq": TensorDecl((spec.q_rank, spec.hidden_size)), "dq.norm": TensorDecl((spec.q_rank,), init="unit"),
+                        "uq": TensorDecl((H * (D + R), spec.q_rank))})
+        else:
+            out["q"] = TensorDecl((H * (D + R), spec.hidden_size))
+        if spec.output_gate:
+            out["g"] = TensorDecl((H * V, spec.hidden_size))
+        return out
 
     def __init__(self, spec: LatentAttentionSpec, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
         super().__init__(spec, tensors, rt)
         self.validate(spec)
         H, D, V, rank = spec.num_heads, spec.head_dim, spec.value_dim, spec.kv_rank
-        self.down = Linear(fuse_rows([tensors["dq"], tensors["dkv"]]), rt)          # columns [c_q raw | c raw | k_rot raw]
-        self.q_norm = tensors["dq.norm"].to(device=rt.device, dtype=torch.float32).contiguous()
+        # one product of the input: columns [c_q raw (or q) | c raw | k_rot raw | gate logits]
+        rows = [tensors["dq"] if spec.q_rank > 0 else tensors["q"], tensors["dkv"]] + ([tensors["g"]] if spec.output_gate else [])
+        self.down = Linear(fuse_rows(rows), rt)
+        self.q_norm = self.up_q = None
+        if spec.q_rank > 0:
+            self.q_norm = tensors["dq.norm"].to(device=rt.device, dtype=torch.float32).contiguous()
+            self.up_q = Linear(tensors["uq"], rt)
         self.kv_norm = tensors["dkv.norm"].to(device=rt.device, dtype=torch.float32).contiguous()
-        self.up_q = Linear(tensors["uq"], rt)
         # W_uk per head, transposed to [H, rank, D]: the product that folds it into the query reads rows of D
         self.uk_t = tensors["uk"].to(device=rt.device, dtype=rt.dtype).view(H, D, rank).transpose(1, 2).contiguous()
         self.uv = tensors["uv"].to(device=rt.device, dtype=rt.dtype).view(H, V, rank).contiguous()
         self.out = Linear(tensors["o"], rt)
-        self.position = part_class("position", spec.position)(spec.position, {}, rt)
-        if getattr(self.position, "frequencies", None) is None or self.position.dims != spec.rot_dim:
-            raise NotImplementedError("latent attention rotates inside its kernels: it takes a position part with "
-                                      "`frequencies` over exactly rot_dim channels")
+        self.position = self.frequencies = None
+        if spec.position is not None:
+            self.position = part_class("position", spec.position)(spec.position, {}, rt)
+            if getattr(self.position, "frequencies", None) is None or self.position.dims != spec.rot_dim:
+                raise NotImplementedError("latent attention rotates inside its kernels: it takes a position part with "
+                                          "`frequencies` over exactly rot_dim channels")
+            self.frequencies = self.position.frequencies
 
     def kv_need(self) -> KVNeed:
         return KVNeed(1, self.spec.kv_rank + self.spec.rot_dim, self.spec.window, values=False)
@@ -72,12 +92,22 @@ class LatentAttention(Mixer):
     def forward(self, x: torch.Tensor, ctx, binding) -> torch.Tensor:
         spec, ops = self.spec, self.rt.ops
         H, D, R, V, rank = spec.num_heads, spec.head_dim, spec.rot_dim, spec.value_dim, spec.kv_rank
-        y = self.down(x)                                                  # [T, q_rank + rank + R]
-        c_q = ops.latent_prepare(y, ctx, binding, spec.q_rank, rank, R, self.q_norm, self.kv_norm, spec.norm_eps,
-                                 self.position.frequencies)              # normed query latent; [c | k_rot] is in the cache
-        q = self.up_q(c_q)                                                # [T, H (D + R)]
+        y = self.down(x)                                                  # [T, (q_rank or H (D + R)) + rank + R (+ H V)]
+        if spec.q_rank > 0:
+            latents = spec.q_rank + rank + R
+            c_q = ops.latent_prepare(y[:, :latents], ctx, binding, spec.q_rank, rank, R, self.q_norm, self.kv_norm,
+                                     spec.norm_eps, self.frequencies)    # normed query latent; [c | k_rot] is in the cache
+            q = self.up_q(c_q)                                            # [T, H (D + R)]
+        else:
+            latents = H * (D + R) + rank + R
+            q = y[:, :H * (D + R)]
+            ops.latent_prepare(y[:, H * (D + R):latents], ctx, binding, 0, rank, R, None, self.kv_norm, spec.norm_eps,
+                               self.frequencies)
         q_lat = ops.per_head_linear(q, self.uk_t, H, D + R, D)            # float32 [T, H, rank]: W_uk^T q_flat
-        o_lat = ops.latent_attention(q_lat, q, ctx, binding, H, D + R, D, rank, R, self.position.frequencies,
+        o_lat = ops.latent_attention(q_lat, q, ctx, binding, H, D + R, D, rank, R, self.frequencies,
                                      spec.scale, spec.window)             # [T, H, rank]: softmax-weighted sums of c
         o = ops.per_head_linear(o_lat.view(-1, H * rank), self.uv, H, rank, rank, out_dtype=x.dtype)   # [T, H, V]
-        return self.out(o.reshape(-1, H * V))
+        o = o.reshape(-1, H * V)
+        if spec.output_gate:
+            o = ops.sigmoid_gate(o, y[:, latents:latents + H * V])
+        return self.out(o)

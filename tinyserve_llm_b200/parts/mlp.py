@@ -1,8 +1,8 @@
 """
 Dense gated feed-forward: down(act(gate(x)) * up(x)), gate and up fused into one projection whose
 output columns are [gate | up].  Activations: silu(g) u (with the products that carry it in their
-epilogue), relu(g) u, and the clamped swish g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit),
-u' = clamp(u, -limit, limit).
+epilogue), relu(g) u, the clamped swish g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit),
+u' = clamp(u, -limit, limit), and the tanh form of gelu, g/2 (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) u.
 
 Reference: model/llama.py:77-83 (silu(gate) * up), :215-225 (fused gate_up, down; no biases).
 """
@@ -22,7 +22,7 @@ from tinyserve_llm_b200.parts.linear import Linear, fuse_rows
 class GatedMLP(FeedForward):
     graph_safe = True
 
-    ACTIVATIONS = ("silu", "relu", "clamped_swish")
+    ACTIVATIONS = ("silu", "relu", "clamped_swish", "gelu_tanh")
 
     @classmethod
     def declare(cls, spec: GatedMLPSpec) -> dict[str, TensorDecl]:

@@ -12,8 +12,8 @@ from __future__ import annotations
 import torch
 
 from tinyserve_llm_b200.config.spec import ModelSpec
-from tinyserve_llm_b200.parts import (attention, delta_rule, gated_attention, latent_attention, mingru, mlp, mlstm,  # noqa: F401  (registration)
-                                      norm, parallel, recurrence, rotary, routed_experts)
+from tinyserve_llm_b200.parts import (attention, delta_rule, differential_attention, gated_attention, latent_attention,  # noqa: F401  (registration)
+                                      mingru, mlp, mlstm, norm, parallel, recurrence, rotary, routed_experts)
 from tinyserve_llm_b200.parts.base import KVNeed, Runtime, TensorDecl, arrangement_class, part_class
 from tinyserve_llm_b200.parts.block import _sub
 from tinyserve_llm_b200.parts.linear import Linear
@@ -29,6 +29,9 @@ def declared_tensors(spec: ModelSpec) -> dict[str, TensorDecl]:
         out[spec.final_norm_prefix + name] = decl
     if spec.lm_head_name is not None:
         out[spec.lm_head_name] = TensorDecl((spec.vocab_size, spec.hidden_size))
+    if spec.embedding_norm is not None:
+        for name, decl in part_class("norm", spec.embedding_norm).declare(spec.embedding_norm).items():
+            out[spec.embedding_norm_prefix + name] = decl
     return out
 
 
@@ -52,6 +55,10 @@ class DecoderModel:
         self.embedding_position = None
         if spec.embedding_position is not None:
             self.embedding_position = part_class("position", spec.embedding_position)(spec.embedding_position, {}, rt)
+        self.embedding_norm = None
+        if spec.embedding_norm is not None:
+            self.embedding_norm = part_class("norm", spec.embedding_norm)(
+                spec.embedding_norm, _sub(tensors, spec.embedding_norm_prefix), rt)
         self._check_run_list()
         # A CUDA graph may replay the model only if no part runs host code that depends on the step.
         self.graph_safe = all(getattr(part, "graph_safe", False) for block in self.blocks
@@ -94,11 +101,15 @@ class DecoderModel:
         scale = float(self.spec.embedding_scale)
         if self.embedding_position is not None and not getattr(first, "takes_embedding_position", False):
             raise NotImplementedError("a position vector on the embedding needs a first block whose arrangement takes it")
+        if self.embedding_norm is not None and not getattr(first, "takes_embedding_norm", False):
+            raise NotImplementedError("a norm on the embedding needs a first block whose arrangement takes it")
         if first is not None and getattr(first, "takes_token_ids", False) and (
                 scale == 1.0 or getattr(first, "takes_embedding_scale", False)):
             extra = {"embedding_scale": scale} if scale != 1.0 else {}
             if self.embedding_position is not None:
                 extra["embedding_position"] = self.embedding_position
+            if self.embedding_norm is not None:
+                extra["embedding_norm"] = self.embedding_norm
             x, residual = first.forward(ctx.token_ids, None, ctx, ctx.binding(run[0]), embedding=self.embedding, **extra)
             run = run[1:]
         elif scale != 1.0:
@@ -113,4 +124,7 @@ class DecoderModel:
                out: torch.Tensor | None = None) -> torch.Tensor:
         """float32 [len(rows), vocab] (into `out` if given): final norm and vocabulary projection of the wanted rows only."""
         h, _ = self.final_norm.forward(x, residual, rows)
-        return self.lm_head(h, out_dtype=torch.float32, out=out)
+        logits = self.lm_head(h, out_dtype=torch.float32, out=out)
+        if self.spec.logit_scale != 1.0 or self.spec.logit_softcap > 0:
+            self.rt.ops.scale_tanh_cap(logits, self.spec.logit_scale, self.spec.logit_softcap)
+        return logits

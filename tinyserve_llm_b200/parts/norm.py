@@ -94,12 +94,18 @@ class StreamRMSNorm(Norm):
         self.rt.ops.stream_norm(branch, self.weight, residual, None, self.eps, self.rt.dtype)
 
     def forward_embedded(self, table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0, positions: torch.Tensor | None = None,
-                         position=None):
-        """`position` (a part with `frequencies`) and `positions`: its vector is added to the scaled rows."""
+                         position=None, start_norm: "StreamRMSNorm | None" = None):
+        """
+        `position` (a part with `frequencies`) and `positions`: its vector is added to the scaled rows.
+        `start_norm` (a stream norm of this norm's kind and eps): the rows are normed by it before they start the stream.
+        """
+        if start_norm is not None and (start_norm.centered != self.centered or start_norm.eps != self.eps):
+            raise NotImplementedError("a norm on the embedding runs inside the first norm's kernel: both must be of one kind and eps")
         residual = torch.empty((ids.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
         out = self.rt.ops.stream_norm(None, None, residual, self.weight, self.eps, self.rt.dtype, table=table, ids=ids,
                                       scale=scale, centered=self.centered, positions=positions,
-                                      position_frequencies=position.frequencies if position is not None else None)
+                                      position_frequencies=position.frequencies if position is not None else None,
+                                      w_start=start_norm.weight if start_norm is not None else None)
         return out, residual
 
 

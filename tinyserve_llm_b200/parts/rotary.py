@@ -68,21 +68,41 @@ def yarn_frequencies(dims: int, base: float, yarn) -> torch.Tensor:
     return freq / yarn.factor * ramp + freq * (1.0 - ramp)
 
 
+def band_scaled_frequencies(dims: int, base: float, bands) -> torch.Tensor:
+    """
+    float64 [dims / 2]: base^(-2i/dims) rescaled by wavelength l = 2 pi / f (`bands`: a `Llama3Scaling`): kept where
+    l < original / high, divided by the factor where l > original / low, and in between, with
+    s = (original / l - low) / (high - low), the blend (1 - s) f / factor + s f.
+    """
+    f = yarn_frequencies(dims, base, None)
+    original, low, high = float(bands.original_max_position_embeddings), float(bands.low_freq_factor), float(bands.high_freq_factor)
+    wavelength = 2 * math.pi / f
+    s = (original / wavelength - low) / (high - low)
+    blend = (1 - s) * f / bands.factor + s * f
+    return torch.where(wavelength < original / high, f, torch.where(wavelength > original / low, f / bands.factor, blend))
+
+
 @register_part("position", "rotary_inline")
 class InlineRotary(PositionEncoding):
     """
     Rotate-half rotation whose angles the kernels compute themselves, position * frequencies[i] in
-    float32 with frequencies[i] = base^(-2i/dims): no table, so no longest position.  Mixers that
-    rotate inside their own kernels read `dims` and `frequencies`.
+    float32 with frequencies[i] = base^(-2i/dims) (rescaled by the spec's `yarn` or `bands`): no table,
+    so no longest position.  Mixers that rotate inside their own kernels read `dims` and `frequencies`.
     """
 
     def __init__(self, spec, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
         super().__init__(spec, tensors, rt)
         if spec.dims <= 0 or spec.dims % 2:
             raise ValueError(f"rotation over {spec.dims} channels: the number must be positive and even")
+        if spec.yarn is not None and getattr(spec, "bands", None) is not None:
+            raise ValueError("a rotation takes one rescaling of its frequencies, YaRN or wavelength bands, not both")
         key = ("rotary_inline", spec)
         if key not in rt.shared:
-            rt.shared[key] = yarn_frequencies(spec.dims, float(spec.base), spec.yarn).to(torch.float32).to(rt.device)
+            if getattr(spec, "bands", None) is not None:
+                freq = band_scaled_frequencies(spec.dims, float(spec.base), spec.bands)
+            else:
+                freq = yarn_frequencies(spec.dims, float(spec.base), spec.yarn)
+            rt.shared[key] = freq.to(torch.float32).to(rt.device)
         self.dims = spec.dims
         self.frequencies = rt.shared[key]
         # cos and sin are multiplied by this (1 without YaRN); a kernel that rotates with a YaRN rescaling has to apply it
