@@ -275,11 +275,11 @@ class _Slots:
             for n in pages_of:
                 tables.append(order[at:at + n]); at += n
             width = max(len(t) for t in tables)
-            vd = need.value_dim or need.head_dim
+            vd, vh = need.value_dim or need.head_dim, getattr(need, "value_heads", 0) or need.num_kv_heads
             k = torch.full((num_pages, 1, need.num_kv_heads, page, need.head_dim), float("nan"), dtype=dtype, device="cuda")
-            v = torch.full((num_pages, 1, need.num_kv_heads, page, vd), float("nan"), dtype=dtype, device="cuda")
+            v = torch.full((num_pages, 1, vh, page, vd), float("nan"), dtype=dtype, device="cuda") if need.values else None
             self.table = _i32([t + [-1] * (width - len(t)) for t in tables])
-            per_k, per_v = need.num_kv_heads * page * need.head_dim, need.num_kv_heads * page * vd
+            per_k, per_v = need.num_kv_heads * page * need.head_dim, vh * page * vd
             self.binding = EntryBinding(k, v, per_k, 0, page, num_pages, None, width, True, 0, self.binding.state, None, per_v, 0)
 
     def step(self, x_of, ranges):

@@ -18,6 +18,11 @@
 //
 // Keys and values beyond the request's length (the unwritten tail of its last page) are zero-filled
 // on load and masked by select, so whatever those slots hold never reaches a result.
+//
+// Options of the mask and of the score (ts_paged_attention_bf16_masked): chunks of n positions outside of
+// which a query sees nothing (it sees keys max(p - window + 1, floor(p / n) n) .. p); scores capped as
+// c tanh(q . k scale / c) before the softmax (the CAP form of the kernels); a value pool with fewer heads than
+// the key pool (key head j reads value head j / (key heads / value heads)) and a geometry of its own.
 #include "attention_bf16.h"
 
 #include "common.cuh"
@@ -44,6 +49,21 @@ __device__ __forceinline__ float fast_exp2_any(float x) {
     asm("ex2.approx.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
+// tanh(x) = 1 - 2 / (e^(2x) + 1), from the exponential and a division (a few ulp; the hardware's approximate
+// tanh keeps 11 bits); beyond +-15 the result is +-1 in float32 anyway.
+__device__ __forceinline__ float exp_tanh(float x) {
+    x = fminf(fmaxf(x, -15.f), 15.f);
+    return 1.f - __fdividef(2.f, 1.f + fast_exp2_any(x * (2.f * LOG2E)));
+}
+// The first key a query at position `pos` sees: inside its window and inside its chunk (0: no such bound).
+__device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (chunk > 0 && pos > 0) lo = max(lo, pos / chunk * chunk);
+    return lo;
+}
+// The forms of the kernels: softmax, sigmoid weights, softmax of capped scores.
+enum { SOFTMAX = 0, SIGMOID = 1, CAPPED = 2 };
+
 // One warp loads a tile whose ROWS rows lie back to back in memory (a head's keys of one page).
 // Lane l takes 16-byte chunk l % CHUNKS of rows l / CHUNKS + j * (32 / CHUNKS): the row is
 // r0 | const_j, so its swizzle is (chunk ^ r0) ^ const_j and every address is one base plus constants.
@@ -87,11 +107,13 @@ struct RowState {
 // over the keys: no maximum, no sum, no rescaling; slope2 and bias2 are the rows' slope and bias times log2(e).
 // The rows' maxima are set to 0, so that the merges of warps and splits, which weigh a share by
 // exp2(its maximum - the largest), add the shares as they are.
-template <int HD, bool MASK, int KT = TILE, bool FIRST = false, bool TOP = false, bool SIG = false>
+// CAPPED: the scores become tanh(s * cap_pre) here (cap_pre = scale / cap) and scale_log2 is cap * log2(e).
+template <int HD, bool MASK, int KT = TILE, bool FIRST = false, bool TOP = false, int FORM = SOFTMAX>
 __device__ __forceinline__ void attend_tile(RowState<HD>& st, const uint32_t (&q)[HD / 16][4], __nv_bfloat16* k_tile,
                                             __nv_bfloat16* v_tile, int key0, const int (&pos)[2], const int (&lo)[2],
                                             float scale_log2, int lane, const float (&slope2)[2] = {0.f, 0.f},
-                                            const float (&bias2)[2] = {0.f, 0.f}) {
+                                            const float (&bias2)[2] = {0.f, 0.f}, float cap_pre = 0.f) {
+    constexpr bool SIG = FORM == SIGMOID;
     float s[KT / 8][4];
 #pragma unroll
     for (int n = 0; n < KT / 8; ++n)
@@ -129,6 +151,12 @@ __device__ __forceinline__ void attend_tile(RowState<HD>& st, const uint32_t (&q
         }
         st.m[0] = st.m[1] = 0.f;
     } else {
+    if (FORM == CAPPED) {
+#pragma unroll
+        for (int n = 0; n < KT / 8; ++n)
+#pragma unroll
+            for (int e = 0; e < (TOP ? 2 : 4); ++e) s[n][e] = exp_tanh(s[n][e] * cap_pre);
+    }
     // mask, running maximum (of raw scores; the scale is positive and joins the exponent below)
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -203,8 +231,12 @@ struct AttnParams {
     const int* cu_q;
     const int* ctx_lens;
     int num_seqs, nh, nkv;
-    float scale_log2;
+    float scale_log2;          // CAPPED: cap * log2(e)
     int window;
+    int chunk;                 // 0: no chunks
+    float cap_pre;             // CAPPED: scale / cap, what the raw product is multiplied by inside the tanh
+    int value_heads;           // heads of the value pool (a divisor of nkv)
+    KVGeometry geo_v;          // the value pool's geometry
     const int* prefill_seqs;   // requests that feed more than one token, for the prefill grid (-1: none); null: every request
     // decode only
     float* partial_o;      // [seq][head][split][HD]
@@ -222,8 +254,9 @@ __device__ __forceinline__ float head_gate(const AttnParams& p, long long token,
 }
 
 // ------------------------------------------------------------------------------------------------ prefill
-template <int HD, bool SIG>
+template <int HD, int FORM>
 __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
+    constexpr bool SIG = FORM == SIGMOID;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);             // [64][HD]
     __nv_bfloat16* kv_tiles = q_tile + TILE * HD;                                     // 2 stages x (K, V) x [64][HD]
@@ -240,6 +273,7 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
     const int pos0 = ctx - q_len + row0;                                              // position of that query
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = head / (p.nh / p.nkv);
+    const int vh = kvh / (p.nkv / p.value_heads);
     const long long row_width = p.q_stride;
     const int* table = p.block_table + (long long)seq * p.table_width;
 
@@ -248,7 +282,7 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
     cp_async_commit();
 
     const int last_pos = pos0 + rows - 1;
-    const int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int first_key = first_visible(pos0, p.window, p.chunk);
     const int kt_begin = first_key / TILE, kt_end = last_pos / TILE + 1;
 
     auto issue = [&](int kt, int stage) {
@@ -256,7 +290,7 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
         __nv_bfloat16* v_tile = k_tile + TILE * HD;
         const int key0 = kt * TILE;
         const __nv_bfloat16* k_src = kv_row<HD>(p.k_pool, p.geo, table, kvh, key0);
-        const __nv_bfloat16* v_src = kv_row<HD>(p.v_pool, p.geo, table, kvh, key0);
+        const __nv_bfloat16* v_src = kv_row<HD>(p.v_pool, p.geo_v, table, vh, key0);
         const int valid = k_src ? min(TILE, ctx - key0) : 0;
         load_tile<HD>(k_tile, k_src ? k_src : p.k_pool, HD, TILE, valid, tid, 128);
         load_tile<HD>(v_tile, v_src ? v_src : p.v_pool, HD, TILE, valid, tid, 128);
@@ -277,7 +311,7 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
     for (int r = 0; r < 2; ++r) {
         const int tile_row = warp * 16 + (lane >> 2) + r * 8;
         pos[r] = tile_row < rows ? pos0 + tile_row : -1;                              // -1: a padding row sees nothing
-        lo[r] = p.window > 0 ? max(0, pos[r] - p.window + 1) : 0;
+        lo[r] = first_visible(pos[r], p.window, p.chunk);
     }
     RowState<HD> st;
     float slope2[2] = {0.f, 0.f}, bias2[2] = {0.f, 0.f};
@@ -288,7 +322,7 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
     // positions of the warp's first and last real row: tiles wholly visible to all 16 rows need no mask
     const int warp_rows = min(rows - warp * 16, 16);
     const int warp_first = pos0 + warp * 16, warp_last = warp_first + warp_rows - 1;
-    const int warp_lo_last = p.window > 0 ? max(0, warp_last - p.window + 1) : 0;
+    const int warp_lo_last = first_visible(warp_last, p.window, p.chunk);
     for (int kt = kt_begin; kt < kt_end; ++kt) {
         const int stage = (kt - kt_begin) & 1;
         cp_async_wait<0>();                  // tile kt has landed (this thread's share)
@@ -298,11 +332,11 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
         const int key0 = kt * TILE;
         if (warp_rows > 0 && key0 <= warp_last) {           // else: all of the warp's rows lie before this tile
             if (warp_rows == 16 && key0 + TILE - 1 <= warp_first && key0 >= warp_lo_last)
-                attend_tile<HD, false, TILE, false, false, SIG>(st, q, k_tile, k_tile + TILE * HD, key0, pos, lo, p.scale_log2,
-                                                                lane, slope2, bias2);
+                attend_tile<HD, false, TILE, false, false, FORM>(st, q, k_tile, k_tile + TILE * HD, key0, pos, lo, p.scale_log2,
+                                                                 lane, slope2, bias2, p.cap_pre);
             else
-                attend_tile<HD, true, TILE, false, false, SIG>(st, q, k_tile, k_tile + TILE * HD, key0, pos, lo, p.scale_log2,
-                                                               lane, slope2, bias2);
+                attend_tile<HD, true, TILE, false, false, FORM>(st, q, k_tile, k_tile + TILE * HD, key0, pos, lo, p.scale_log2,
+                                                                lane, slope2, bias2, p.cap_pre);
         }
     }
     // rows' sums over the quad, then write
@@ -325,8 +359,9 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
 }
 
 // ------------------------------------------------------------------------------------------------ decode
-template <int HD, bool SIG>
+template <int HD, int FORM>
 __global__ void __launch_bounds__(DW * 32) decode_attention_kernel(AttnParams p) {
+    constexpr bool SIG = FORM == SIGMOID;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
     // Before the wait for the kernel ahead on the stream: what does not depend on it.  The index
@@ -343,7 +378,7 @@ __global__ void __launch_bounds__(DW * 32) decode_attention_kernel(AttnParams p)
     const int ctx = p.ctx_lens[seq];
     const int pos = ctx - 1;
     const int g = p.nh / p.nkv;
-    const int first_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int first_key = first_visible(pos, p.window, p.chunk);
     const int key_begin = split * SPLIT;
     const bool active = decoding && key_begin <= pos && key_begin + SPLIT > first_key;
     float* part_o = p.partial_o + (((long long)seq * p.nh + kvh * g) * p.max_splits + split) * HD;
@@ -368,7 +403,7 @@ __global__ void __launch_bounds__(DW * 32) decode_attention_kernel(AttnParams p)
     int valid = 0;
     if (warp_active) {
         k_src = kv_row_of_page<HD>(p.k_pool, p.geo, page0, kvh, key0);
-        v_src = kv_row_of_page<HD>(p.v_pool, p.geo, page0, kvh, key0);
+        v_src = kv_row_of_page<HD>(p.v_pool, p.geo_v, page0, kvh / (p.nkv / p.value_heads), key0);
         valid = k_src ? min(DKT, ctx - key0) : 0;
         if (!holds_new) {
             if (k_src) {
@@ -415,11 +450,11 @@ __global__ void __launch_bounds__(DW * 32) decode_attention_kernel(AttnParams p)
             }
         }
         if (g <= 8) {
-            if (masked) attend_tile<HD, true, DKT, true, true, SIG>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane, slope2, bias2);
-            else attend_tile<HD, false, DKT, true, true, SIG>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane, slope2, bias2);
+            if (masked) attend_tile<HD, true, DKT, true, true, FORM>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane, slope2, bias2, p.cap_pre);
+            else attend_tile<HD, false, DKT, true, true, FORM>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane, slope2, bias2, p.cap_pre);
         } else {
-            if (masked) attend_tile<HD, true, DKT, true, false, SIG>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane, slope2, bias2);
-            else attend_tile<HD, false, DKT, true, false, SIG>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane, slope2, bias2);
+            if (masked) attend_tile<HD, true, DKT, true, false, FORM>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane, slope2, bias2, p.cap_pre);
+            else attend_tile<HD, false, DKT, true, false, FORM>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane, slope2, bias2, p.cap_pre);
         }
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -548,11 +583,12 @@ __global__ void __launch_bounds__(GROUPS * HD) decode_combine_kernel(AttnParams 
         __float2bfloat16_rn(SIG ? o * head_gate(p, q_begin, head) : (l > 0.f ? o / l : 0.f));
 }
 
-template <int HD, bool SIG>
+template <int HD, int FORM>
 int launch(const AttnParams& p, int max_q_len, int min_q_len, int max_ctx_len, int num_prefill_seqs, cudaStream_t stream) {
     if (max_q_len > 1) {
         const size_t smem = (size_t)(TILE * HD + 4 * TILE * HD) * sizeof(__nv_bfloat16);
-        auto kernel = prefill_attention_kernel<HD, SIG>;
+        constexpr bool SIG = FORM == SIGMOID;
+        auto kernel = prefill_attention_kernel<HD, FORM>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         dim3 grid((max_q_len + TILE - 1) / TILE, p.nh, p.prefill_seqs ? num_prefill_seqs : p.num_seqs);
         kernel<<<grid, 128, smem, stream>>>(p);
@@ -562,7 +598,8 @@ int launch(const AttnParams& p, int max_q_len, int min_q_len, int max_ctx_len, i
         const size_t tiles = (size_t)(16 + DW * 2 * DKT) * HD * sizeof(__nv_bfloat16);
         const size_t merge = (size_t)(DW * 16 * (HD + 8) + DW * 16 * 2) * sizeof(float);
         const size_t smem = tiles > merge ? tiles : merge;
-        auto kernel = decode_attention_kernel<HD, SIG>;
+        constexpr bool SIG = FORM == SIGMOID;
+        auto kernel = decode_attention_kernel<HD, FORM>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         const int splits = (max_ctx_len + SPLIT - 1) / SPLIT;
         if (splits > p.max_splits) return ts_fail("decode_attention: %d splits needed, scratch holds %d", splits, p.max_splits);
@@ -599,11 +636,16 @@ int run(const void* q, long long q_stride, void* out, const void* k_pool, const 
         const int* ctx_lens, int num_seqs, int max_q_len, int min_q_len, int max_ctx_len, int nh, int nkv, int hd,
         float scale, int window, float* scratch, long long scratch_floats, const int* prefill_seqs, int num_prefill_seqs,
         bool sigmoid, const float* slopes, const float* head_bias, const void* gate, long long gate_stride,
-        cudaStream_t stream) {
+        cudaStream_t stream, int chunk = 0, float softcap = 0.f, int value_heads = 0, long long v_page_stride = -1,
+        long long v_entry_offset = -1) {
     TS_REQUIRE(ts_attention_bf16_supported(hd, page_tokens, nh, nkv),
                "paged_attention_bf16: head_dim %d / page %d / heads %d:%d is not taken by the tensor-core kernels", hd,
                page_tokens, nh, nkv);
-    TS_REQUIRE(num_seqs >= 0 && max_q_len >= min_q_len && window >= 0, "paged_attention_bf16: bad sizes");
+    TS_REQUIRE(num_seqs >= 0 && max_q_len >= min_q_len && window >= 0 && chunk >= 0 && softcap >= 0.f,
+               "paged_attention_bf16: bad sizes");
+    TS_REQUIRE(value_heads >= 0 && (value_heads == 0 || nkv % value_heads == 0),
+               "paged_attention_bf16: %d value heads do not divide %d key heads", value_heads, nkv);
+    TS_REQUIRE(!(sigmoid && softcap > 0.f), "paged_attention_bf16: capped scores come with softmax weights");
     TS_REQUIRE(num_seqs <= 65535 && nh <= 65535, "paged_attention_bf16: more than 65535 requests or heads in a step");
     if (num_seqs == 0 || max_q_len <= 0) return 0;
     AttnParams p;
@@ -624,8 +666,12 @@ int run(const void* q, long long q_stride, void* out, const void* k_pool, const 
     p.num_seqs = num_seqs;
     p.nh = nh;
     p.nkv = nkv;
-    p.scale_log2 = scale * LOG2E;
+    p.scale_log2 = softcap > 0.f ? softcap * LOG2E : scale * LOG2E;
+    p.cap_pre = softcap > 0.f ? scale / softcap : 0.f;
     p.window = window;
+    p.chunk = chunk;
+    p.value_heads = value_heads > 0 ? value_heads : nkv;
+    p.geo_v = v_page_stride >= 0 ? KVGeometry{v_page_stride, v_entry_offset, page_tokens, num_pages} : p.geo;
     p.max_splits = (max_ctx_len + SPLIT - 1) / SPLIT;
     p.prefill_seqs = prefill_seqs;
     TS_REQUIRE(prefill_seqs == nullptr || (num_prefill_seqs >= 0 && num_prefill_seqs <= num_seqs),
@@ -640,11 +686,15 @@ int run(const void* q, long long q_stride, void* out, const void* k_pool, const 
                    "paged_attention_bf16: block tables of %d pages do not reach %d tokens", table_width, max_ctx_len);
     }
     if (sigmoid) {
-        if (hd == 64) return launch<64, true>(p, max_q_len, min_q_len, max_ctx_len, num_prefill_seqs, stream);
-        return launch<128, true>(p, max_q_len, min_q_len, max_ctx_len, num_prefill_seqs, stream);
+        if (hd == 64) return launch<64, SIGMOID>(p, max_q_len, min_q_len, max_ctx_len, num_prefill_seqs, stream);
+        return launch<128, SIGMOID>(p, max_q_len, min_q_len, max_ctx_len, num_prefill_seqs, stream);
     }
-    if (hd == 64) return launch<64, false>(p, max_q_len, min_q_len, max_ctx_len, num_prefill_seqs, stream);
-    return launch<128, false>(p, max_q_len, min_q_len, max_ctx_len, num_prefill_seqs, stream);
+    if (softcap > 0.f) {
+        if (hd == 64) return launch<64, CAPPED>(p, max_q_len, min_q_len, max_ctx_len, num_prefill_seqs, stream);
+        return launch<128, CAPPED>(p, max_q_len, min_q_len, max_ctx_len, num_prefill_seqs, stream);
+    }
+    if (hd == 64) return launch<64, SOFTMAX>(p, max_q_len, min_q_len, max_ctx_len, num_prefill_seqs, stream);
+    return launch<128, SOFTMAX>(p, max_q_len, min_q_len, max_ctx_len, num_prefill_seqs, stream);
 }
 
 }  // namespace
@@ -673,4 +723,21 @@ TS_API int ts_paged_attention_bf16_sigmoid(const void* q, long long q_stride, vo
     return run(q, q_stride, out, k_pool, v_pool, page_stride, entry_offset, page_tokens, num_pages, block_table, table_width,
                cu_q, ctx_lens, num_seqs, max_q_len, min_q_len, max_ctx_len, nh, nkv, hd, scale, window, scratch,
                scratch_floats, prefill_seqs, num_prefill_seqs, true, slopes, head_bias, gate, gate_stride, stream);
+}
+
+// Softmax attention with the options of the mask and of the score: chunks, capped scores, a value pool of
+// `value_heads` heads (0: as many as key heads) with a geometry of its own.  Queries in a matrix of their own.
+TS_API int ts_paged_attention_bf16_masked(const void* q, long long q_stride, void* out, const void* k_pool,
+                                          const void* v_pool, long long page_stride, long long entry_offset,
+                                          long long v_page_stride, long long v_entry_offset, int page_tokens, int num_pages,
+                                          const int* block_table, int table_width, const int* cu_q, const int* ctx_lens,
+                                          int num_seqs, int max_q_len, int min_q_len, int max_ctx_len, int nh, int nkv,
+                                          int hd, float scale, int window, int chunk, float softcap, int value_heads,
+                                          float* scratch, long long scratch_floats, const int* prefill_seqs,
+                                          int num_prefill_seqs, cudaStream_t stream) {
+    TS_REQUIRE(q_stride % 8 == 0 && (uintptr_t)q % 16 == 0, "paged_attention_bf16: query rows must start on 16-byte boundaries");
+    return run(q, q_stride, out, k_pool, v_pool, page_stride, entry_offset, page_tokens, num_pages, block_table, table_width,
+               cu_q, ctx_lens, num_seqs, max_q_len, min_q_len, max_ctx_len, nh, nkv, hd, scale, window, scratch,
+               scratch_floats, prefill_seqs, num_prefill_seqs, false, nullptr, nullptr, nullptr, 0, stream, chunk, softcap,
+               value_heads, v_page_stride, v_entry_offset);
 }

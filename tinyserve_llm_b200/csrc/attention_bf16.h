@@ -37,6 +37,18 @@ int ts_paged_attention_bf16_sigmoid(const void* q, long long q_stride, void* out
                                     const int* prefill_seqs, int num_prefill_seqs, const float* slopes,
                                     const float* head_bias, const void* gate, long long gate_stride, cudaStream_t stream);
 
+// Softmax attention with options of the mask and of the score: `chunk` n > 0 hides every key before
+// floor(i / n) * n from query i, `softcap` c > 0 turns the scaled product into c tanh(. / c), `value_heads` g > 0
+// says that the value pool holds g heads (key head j reads value head j / (nkv / g)); the value pool has a geometry
+// of its own.  Queries in a matrix of their own, q_stride elements a row.
+int ts_paged_attention_bf16_masked(const void* q, long long q_stride, void* out, const void* k_pool, const void* v_pool,
+                                   long long page_stride, long long entry_offset, long long v_page_stride,
+                                   long long v_entry_offset, int page_tokens, int num_pages, const int* block_table,
+                                   int table_width, const int* cu_q, const int* ctx_lens, int num_seqs, int max_q_len,
+                                   int min_q_len, int max_ctx_len, int nh, int nkv, int hd, float scale, int window,
+                                   int chunk, float softcap, int value_heads, float* scratch, long long scratch_floats,
+                                   const int* prefill_seqs, int num_prefill_seqs, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

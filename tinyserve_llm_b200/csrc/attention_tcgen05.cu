@@ -163,6 +163,22 @@ __device__ __forceinline__ float fast_rcp(float x) {
     asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
+// tanh(x) = 1 - 2 / (e^(2x) + 1) from the exponential and the reciprocal (the hardware's approximate tanh keeps 11
+// bits); beyond +-15 the result is +-1 in float32 anyway.
+__device__ __forceinline__ float exp_tanh(float x) {
+    x = fminf(fmaxf(x, -15.f), 15.f);
+    return fmaf(-2.f, fast_rcp(1.f + fast_exp2_any(x * (2.f * LOG2E))), 1.f);
+}
+// The first key a query at position `pos` sees: inside its window and inside its chunk (0: no such bound).
+__device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (chunk > 0 && pos > 0) lo = max(lo, pos / chunk * chunk);
+    return lo;
+}
+// The forms of the kernel: softmax over every earlier key; sigmoid weights (with a window); softmax behind a mask with
+// a lower bound (window, chunks), of scores that may be capped, over a value pool that may hold fewer heads.
+enum { PLAIN = 0, SIGMOID = 1, BOUNDED = 2 };
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -196,17 +212,24 @@ struct FlashParams {
     const float* head_bias;           // [nh]: added to every score of the head
     const __nv_bfloat16* gate;        // [T, nh] logits, gate_stride elements a row: the head's output times their sigmoid
     long long gate_stride;
+    // the BOUNDED kernel
+    int chunk;                        // n > 0: a query sees no key before floor(p / n) * n
+    float cap_pre;                    // scores are capped: tanh(product * cap_pre), and scale_log2 is cap * log2(e); 0: not capped
+    int value_heads;                  // heads of the value pool (a divisor of nkv)
 };
 
 // SIG: a visible key's weight is sigmoid(score * scale - slope (position - key) + bias): no maximum, no sum, no
 // rescaling, nothing exchanged between the two threads of a row; the epilogue multiplies by the head's gate.
-// Only this form takes a window: its first key tile is the one that holds the first key the tile's first query sees.
-template <int HD, bool SIG>
+// This form and BOUNDED take a window: the first key tile is the one that holds the first key the tile's first query sees.
+// BOUNDED: softmax as in the plain form; a row's keys begin at first_visible(position); capped scores go through
+// tanh in registers before the maximum is taken.
+template <int HD, int FORM>
 __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                         const __grid_constant__ CUtensorMap map_k,
                                                                         const __grid_constant__ CUtensorMap map_v,
                                                                         FlashParams p) {
     using S_ = Shape<HD>;
+    constexpr bool SIG = FORM == SIGMOID, LOW = FORM == BOUNDED;
     constexpr int KEYS = S_::KEYS, SUBS = S_::SUBS, SUB_Q = S_::SUB_Q, SUB_KV = S_::SUB_KV, Q_BYTES = S_::Q_BYTES,
                   KV_BYTES = S_::KV_BYTES, STAGE_BYTES = S_::STAGE_BYTES, O_COL = S_::O_COL, P_COL = S_::P_COL;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -233,9 +256,12 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
     const int pos0 = ctx - q_len + row0;             // position of the tile's first query
     const int last_pos = pos0 + rows - 1;
     const int num_kv = last_pos / KEYS + 1;
-    const int first_seen = SIG && p.window > 0 ? max(0, pos0 - p.window + 1) : 0;     // the first key any row of the tile sees
+    // the first key any row of the tile sees
+    const int first_seen = LOW ? first_visible(pos0, p.window, p.chunk) : (SIG && p.window > 0 ? max(0, pos0 - p.window + 1) : 0);
+    const int low_last = LOW ? first_visible(last_pos, p.window, p.chunk) : 0;         // ... and the first key its last row sees
     const int kv_begin = first_seen / KEYS;          // tiles kv_begin .. num_kv - 1; `it` counts them from 0 for stages and parities
     const int kvh = head / (p.nh / p.nkv);
+    const int nv = LOW ? p.value_heads : p.nkv, vh = LOW ? kvh / (p.nkv / p.value_heads) : kvh;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* table = p.block_table + (long long)seq * p.table_width;
 
@@ -285,10 +311,11 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
                 int page = table[min(key / p.page_tokens, p.table_width - 1)];
                 if (page < 0 || page >= p.num_pages) page = 0;     // given back or beyond the request: masked anyway
                 const int row = ((page * p.entries + p.entry) * p.nkv + kvh) * p.page_tokens + key % p.page_tokens;
+                const int v_row = ((page * p.entries + p.entry) * nv + vh) * p.page_tokens + key % p.page_tokens;
 #pragma unroll
                 for (int h = 0; h < SUBS; ++h) {
                     tma_load_2d(k_tile + h * SUB_KV + b * (64 * 128), &map_k, &kv_full[s], h * 64, row);
-                    tma_load_2d(v_tile + h * SUB_KV + b * (64 * 128), &map_v, &kv_full[s], h * 64, row);
+                    tma_load_2d(v_tile + h * SUB_KV + b * (64 * 128), &map_v, &kv_full[s], h * 64, v_row);
                 }
             }
         }
@@ -346,7 +373,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
         const int col0 = half * HK;
         float m_run = -INFINITY, l_run = 0.f;
         // SIG: the row's first visible key, and the score's terms that do not depend on the key, in powers of two
-        const int lo = SIG && p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        const int lo = LOW ? first_visible(pos, p.window, p.chunk) : (SIG && p.window > 0 ? max(0, pos - p.window + 1) : 0);
         const float slope2 = SIG && p.slopes ? p.slopes[head] * LOG2E : 0.f;
         const float bias2 = (SIG && p.head_bias ? p.head_bias[head] * LOG2E : 0.f) - slope2 * (float)pos;
         bool ok = true;
@@ -364,7 +391,8 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             // some row of the tile does not see all of these keys (beyond its own position, or before its window)
-            const bool masked = key0 + KEYS - 1 > pos0 || (SIG && p.window > 0 && key0 < last_pos - p.window + 1);
+            const bool masked = key0 + KEYS - 1 > pos0 || (SIG && p.window > 0 && key0 < last_pos - p.window + 1) ||
+                                (LOW && key0 < low_last);
             // this thread's keys of S come into registers once, all loads under way together
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             uint32_t sv[HK / 32][32];
@@ -416,6 +444,15 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 mbar_arrive(&p_ready);
             } else {
+            if constexpr (LOW) {
+                if (p.cap_pre != 0.f) {              // capped scores: tanh(product * scale / cap); the cap joins the exponent's scale
+#pragma unroll
+                    for (int ch = 0; ch < HK / 32; ++ch)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            sv[ch][i] = __float_as_uint(exp_tanh(__uint_as_float(sv[ch][i]) * p.cap_pre));
+                }
+            }
             // pass 1: the maximum over them (four running maxima: no long dependent chain)
 #pragma unroll
             for (int ch = 0; ch < HK / 32; ++ch) {
@@ -423,7 +460,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
                 if (masked) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        if (key0 + c + i <= pos) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[ch][i]));
+                        if (key0 + c + i <= pos && (!LOW || key0 + c + i >= lo)) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[ch][i]));
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[ch][i]));
@@ -465,8 +502,8 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
                     for (int i = 0; i < 32; i += 2) {
                         float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use));
                         float p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_use));
-                        if (key0 + c + i > pos) p0 = 0.f;
-                        if (key0 + c + i + 1 > pos) p1 = 0.f;
+                        if (key0 + c + i > pos || (LOW && key0 + c + i < lo)) p0 = 0.f;
+                        if (key0 + c + i + 1 > pos || (LOW && key0 + c + i + 1 < lo)) p1 = 0.f;
                         l4[(i >> 1) & 3] += p0 + p1;
                         packed[i >> 1] = pack_bf16(p0, p1);
                     }
@@ -501,8 +538,9 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
                     tmem_st32(lane_addr + O_COL + c, v);
                 }
             }
-            // value rows beyond the request's length hold whatever the page held: zero them before they are multiplied
-            if (half == 0 && r < KEYS && key0 + KEYS > ctx && key0 + r >= ctx) {
+            // value rows beyond the request's length (BOUNDED: or before the first key the tile sees, whose page may have
+            // been given back) hold whatever the page held: zero them before they are multiplied
+            if (half == 0 && r < KEYS && ((key0 + KEYS > ctx && key0 + r >= ctx) || (LOW && key0 + r < first_seen))) {
 #pragma unroll
                 for (int h = 0; h < SUBS; ++h) {
                     unsigned char* v_row = kv_tiles + s * STAGE_BYTES + KV_BYTES + h * SUB_KV + r * 128;
@@ -599,10 +637,13 @@ int run_prefill(const void* q, long long q_cols, long long q_stride, void* out, 
                 int num_pages, int entries, int entry, int page_tokens, const int* block_table, int table_width,
                 const int* cu_q, const int* ctx_lens, int num_seqs, int num_tokens, int max_q_len, int nh, int nkv, int hd,
                 float scale, const int* prefill_seqs, int num_prefill_seqs, int* error, bool sigmoid, int window,
-                const float* slopes, const float* head_bias, const void* gate, long long gate_stride, cudaStream_t stream) {
+                const float* slopes, const float* head_bias, const void* gate, long long gate_stride, cudaStream_t stream,
+                bool bounded = false, int chunk = 0, float softcap = 0.f, int value_heads = 0) {
     TS_REQUIRE(ts_attention_tcgen05_supported(hd, page_tokens, nh, nkv, 0), "attention_tcgen05: sizes not taken (head_dim %d, page %d)", hd, page_tokens);
-    TS_REQUIRE(sigmoid || window == 0, "attention_tcgen05: only the sigmoid form takes a window");
-    TS_REQUIRE(window >= 0, "attention_tcgen05: a negative window");
+    TS_REQUIRE(sigmoid || bounded || window == 0, "attention_tcgen05: the plain form takes no window");
+    TS_REQUIRE(window >= 0 && chunk >= 0 && softcap >= 0.f, "attention_tcgen05: a negative window, chunk or cap");
+    if (value_heads <= 0) value_heads = nkv;
+    TS_REQUIRE(nkv % value_heads == 0, "attention_tcgen05: %d value heads do not divide %d key heads", value_heads, nkv);
     TS_REQUIRE(error != nullptr, "attention_tcgen05: an error word is needed");
     TS_REQUIRE(num_seqs <= 65535 && (max_q_len + QROWS - 1) / QROWS <= 65535,
                "attention_tcgen05: more than 65535 requests, or tiles of a request, in a step");
@@ -617,7 +658,7 @@ int run_prefill(const void* q, long long q_cols, long long q_stride, void* out, 
     CUtensorMap map_q, map_k, map_v;
     if (make_map(&map_q, q, num_tokens, q_cols, q_stride, QROWS)) return 1;
     if (make_map(&map_k, k_pool, pool_rows, hd, hd, 64)) return 1;
-    if (make_map(&map_v, v_pool, pool_rows, hd, hd, 64)) return 1;
+    if (make_map(&map_v, v_pool, pool_rows / nkv * value_heads, hd, hd, 64)) return 1;
     FlashParams p;
     p.out = (__nv_bfloat16*)out;
     p.block_table = block_table;
@@ -631,7 +672,10 @@ int run_prefill(const void* q, long long q_cols, long long q_stride, void* out, 
     p.num_pages = num_pages;
     p.entries = entries;
     p.entry = entry;
-    p.scale_log2 = scale * LOG2E;
+    p.scale_log2 = softcap > 0.f ? softcap * LOG2E : scale * LOG2E;
+    p.cap_pre = softcap > 0.f ? scale / softcap : 0.f;
+    p.chunk = chunk;
+    p.value_heads = value_heads;
     p.error = error;
     p.window = window;
     p.slopes = slopes;
@@ -639,17 +683,19 @@ int run_prefill(const void* q, long long q_cols, long long q_stride, void* out, 
     p.gate = (const __nv_bfloat16*)gate;
     p.gate_stride = gate_stride;
     dim3 grid(nh, (max_q_len + QROWS - 1) / QROWS, prefill_seqs ? num_prefill_seqs : num_seqs);
-#define TS_FLASH_LAUNCH(HD, SIG)                                                                                          \
+#define TS_FLASH_LAUNCH(HD, FORM)                                                                                         \
     do {                                                                                                                  \
         const size_t smem = (size_t)Shape<HD>::Q_BYTES + 2 * Shape<HD>::STAGE_BYTES + 1024;                               \
-        auto kernel = prefill_attention_tcgen05_kernel<HD, SIG>;                                                          \
+        auto kernel = prefill_attention_tcgen05_kernel<HD, FORM>;                                                         \
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                             \
         TS_CHAINED_CHECK("attention_tcgen05", launch_chained(kernel, grid, dim3(THREADS), smem, stream, map_q, map_k, map_v, p)); \
     } while (0)
-    if (hd == 64 && sigmoid) TS_FLASH_LAUNCH(64, true);
-    else if (hd == 64) TS_FLASH_LAUNCH(64, false);
-    else if (sigmoid) TS_FLASH_LAUNCH(128, true);
-    else TS_FLASH_LAUNCH(128, false);
+    if (hd == 64 && sigmoid) TS_FLASH_LAUNCH(64, SIGMOID);
+    else if (hd == 64 && bounded) TS_FLASH_LAUNCH(64, BOUNDED);
+    else if (hd == 64) TS_FLASH_LAUNCH(64, PLAIN);
+    else if (sigmoid) TS_FLASH_LAUNCH(128, SIGMOID);
+    else if (bounded) TS_FLASH_LAUNCH(128, BOUNDED);
+    else TS_FLASH_LAUNCH(128, PLAIN);
 #undef TS_FLASH_LAUNCH
     return 0;
 }
@@ -685,4 +731,21 @@ TS_API int ts_prefill_attention_tcgen05_sigmoid(const void* q, long long q_strid
     return run_prefill(q, (long long)nh * hd, q_stride, out, k_pool, v_pool, num_pages, entries, entry, page_tokens,
                        block_table, table_width, cu_q, ctx_lens, num_seqs, num_tokens, max_q_len, nh, nkv, hd, scale,
                        prefill_seqs, num_prefill_seqs, error, true, window, slopes, head_bias, gate, gate_stride, stream);
+}
+
+// Softmax attention behind a mask with a lower bound: query i sees keys max(i - window + 1, floor(i / chunk) chunk) .. i
+// (0: no such bound); `softcap` c > 0 turns the scaled product into c tanh(. / c); the value pool holds `value_heads`
+// heads (0: as many as key heads; key head j reads value head j / (nkv / value_heads)) in the same pages and entries.
+// Queries [T, nh * hd] in a matrix of their own, q_stride elements a row.
+TS_API int ts_prefill_attention_tcgen05_masked(const void* q, long long q_stride, void* out, const void* k_pool,
+                                               const void* v_pool, int num_pages, int entries, int entry, int page_tokens,
+                                               const int* block_table, int table_width, const int* cu_q,
+                                               const int* ctx_lens, int num_seqs, int num_tokens, int max_q_len, int nh,
+                                               int nkv, int hd, float scale, int window, int chunk, float softcap,
+                                               int value_heads, const int* prefill_seqs, int num_prefill_seqs, int* error,
+                                               cudaStream_t stream) {
+    return run_prefill(q, (long long)nh * hd, q_stride, out, k_pool, v_pool, num_pages, entries, entry, page_tokens,
+                       block_table, table_width, cu_q, ctx_lens, num_seqs, num_tokens, max_q_len, nh, nkv, hd, scale,
+                       prefill_seqs, num_prefill_seqs, error, false, window, nullptr, nullptr, nullptr, 0, stream, true, chunk,
+                       softcap, value_heads);
 }

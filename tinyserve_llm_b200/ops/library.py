@@ -30,7 +30,9 @@ _SIGNATURES = {
     "ts_paged_attention_bf16": ("int", "pppplliipippiiiiiiifiplpip"),
     "ts_paged_attention_generic": ("int", "pppplliipippiiiifiip"),
     "ts_paged_attention_bf16_sigmoid": ("int", "pl" "ppp" "lliipippiiiiiiifiplpi" "pppl" "p"),
+    "ts_paged_attention_bf16_masked": ("int", "pl" "ppp" "lllliipippiiiiiiifiifi" "plpi" "p"),
     "ts_attention_tcgen05_supported": ("int", "iiiii"),
+    "ts_prefill_attention_tcgen05_masked": ("int", "pl" "ppp" "iiiipippiiiiiifiifi" "pipp"),
     "ts_prefill_attention_tcgen05": ("int", "ppppiiiipippiiiiiifpipp"),
     "ts_prefill_attention_tcgen05_sigmoid": ("int", "pl" "ppp" "iiiipippiiiiiifi" "pppl" "pipp"),
     "ts_embedding": ("int", "pppiiiip"),
@@ -646,6 +648,45 @@ class Ops:
             raise KernelError("paged_attention_split: the head gate must be a [T, heads] stretch of the activation dtype")
         out = torch.empty((q.shape[0], nh * vd), dtype=torch.float32 if out_f32 else q.dtype, device=q.device)
         plain = softcap == 0 and chunk == 0 and value_heads == 0 and not out_f32
+        if (weights == "softmax" and slopes is None and head_bias is None and head_gate is None and not out_f32
+                and self.tensor_core_attention(q, binding, nh, nkv, hd, vd, ctx)):
+            # the tensor-core kernels with the mask's and the score's options: tiles of a prompt's portion, split keys
+            # for requests that feed one token
+            num_seqs = ctx.ctx_lens.shape[0]
+            prefill_seqs = getattr(ctx, "prefill_seqs", None)
+            num_prefill = prefill_seqs.shape[0] if prefill_seqs is not None else 0
+            decode_ctx = getattr(ctx, "max_decode_ctx_len", ctx.max_ctx_len)
+            scratch, floats = None, 0
+            if ctx.min_q_len <= 1:
+                floats = self.lib.ts_attention_bf16_scratch_floats(num_seqs, nh, hd, decode_ctx)
+                key = ("attention", floats)
+                scratch = ctx.scratch.get(key)
+                if scratch is None:
+                    scratch = ctx.scratch[key] = torch.empty((floats,), dtype=torch.float32, device=q.device)
+            max_q_len = ctx.max_q_len
+            if (max_q_len > 1 and self.tcgen05_attention and self.lib.ts_attention_tcgen05_supported(
+                    hd, binding.page_tokens, nh, nkv, 0)):
+                # prompt portions on the tcgen05 kernel; requests that feed one token stay with the split-key kernels
+                per_entry = nkv * binding.page_tokens * hd
+                self._call("ts_prefill_attention_tcgen05_masked", _ptr(q), q.stride(0), _ptr(out), _ptr(binding.k_pool),
+                           _ptr(binding.v_pool), binding.num_pages, binding.page_stride // per_entry,
+                           binding.entry_offset // per_entry, binding.page_tokens, _ptr(binding.block_table),
+                           binding.table_width, _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), num_seqs, q.shape[0], max_q_len, nh, nkv,
+                           hd, scale, window, int(chunk), float(softcap), int(value_heads), _ptr(prefill_seqs), num_prefill,
+                           self.error_word().data_ptr(), _stream())
+                if ctx.min_q_len > 1:
+                    return out
+                max_q_len = 1
+            v_page_stride, v_entry_offset = binding.value_geometry()
+            self._call("ts_paged_attention_bf16_masked", _ptr(q), q.stride(0), _ptr(out), _ptr(binding.k_pool),
+                       _ptr(binding.v_pool), binding.page_stride, binding.entry_offset, v_page_stride, v_entry_offset,
+                       binding.page_tokens, binding.num_pages, _ptr(binding.block_table), binding.table_width, _ptr(ctx.cu_q),
+                       _ptr(ctx.ctx_lens), num_seqs, max_q_len, min(ctx.min_q_len, max_q_len), decode_ctx, nh, nkv, hd, scale, window,
+                       int(chunk), float(softcap), int(value_heads), _ptr(scratch), floats, _ptr(prefill_seqs), num_prefill,
+                       _stream())
+            if ctx.min_q_len <= 1:
+                self.launches += 1 if max_q_len <= 1 else 2          # decode + combine (+ prefill) in one call
+            return out
         if (plain and weights == "sigmoid" and hd == vd and q.dtype == torch.bfloat16 and getattr(ctx, "cu_q", None) is not None
                 and q.stride(0) % 8 == 0 and self.lib.ts_attention_bf16_supported(hd, binding.page_tokens, nh, nkv)):
             # the tensor-core kernels: tiles of a prompt's portion, split keys for requests that feed one token
@@ -693,6 +734,12 @@ class Ops:
                    head_gate.stride(0) if head_gate is not None else 0, float(softcap), int(chunk), int(value_heads),
                    1 if out_f32 else 0, _stream())
         return out
+
+    def tensor_core_attention(self, q: torch.Tensor, binding, nh: int, nkv: int, hd: int, vd: int, ctx=None) -> bool:
+        """Whether the bfloat16 tensor-core attention kernels take these sizes (else the generic kernel runs)."""
+        return bool(hd == vd and q.dtype == torch.bfloat16 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
+                    and (ctx is None or getattr(ctx, "cu_q", None) is not None)
+                    and self.lib.ts_attention_bf16_supported(hd, binding.page_tokens, nh, nkv))
 
     def difference_head_norm(self, maps: torch.Tensor, ctx, heads: int, kv_heads: int, vdim: int, weight: float, eps: float,
                              out_scale: float, dtype: torch.dtype) -> torch.Tensor:

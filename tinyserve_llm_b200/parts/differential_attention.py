@@ -13,7 +13,8 @@ For the attention kernels a map is a head: 2 x heads query heads, 2 x kv heads k
 heads (`value_heads` of the kernels: a query head's value head is its key head's index without the map).
 So that the query heads of one key head lie side by side, as grouped-query attention has them, the rows of
 W_q (and b_q) are put into the order [kv head][map][head of the group] when the part is built; the maps'
-outputs come back in that order (float32, so that the difference is taken of unrounded numbers) and one
+outputs come back in that order (float32 from the generic kernel, so that the difference is taken of
+unrounded numbers; bfloat16 from the tensor-core kernels) and one
 kernel takes the difference and the norm and writes the heads in their own order.  lambda is worked out
 once, in float64, from the four tensors.  Keys of both maps and values live in the paged cache, the value pool
 with half as many heads as the key pool.
@@ -101,7 +102,9 @@ class DifferentialAttention(Mixer):
         y = self.proj(x)                                                # [q (maps grouped) | k | v]
         q = ops.qk_norm_rope_store(y, (0, nq, nq + nk), self.biases, None, s.norm_eps, self.position, ctx, binding,
                                    MAPS * H, MAPS * G, D, V, value_heads=G)
+        # the generic kernel leaves the maps unrounded; the tensor-core kernels (sizes they take, bfloat16) write bfloat16
+        precise = None if ops.tensor_core_attention(q, binding, MAPS * H, MAPS * G, D, V, ctx) else torch.float32
         maps = ops.paged_attention_split(q, ctx, binding, MAPS * H, MAPS * G, D, V, s.scale, s.window, softcap=s.softcap,
-                                         chunk=s.chunk, value_heads=G, out_dtype=torch.float32)
+                                         chunk=s.chunk, value_heads=G, out_dtype=precise)
         o = ops.difference_head_norm(maps, ctx, H, G, V, self.weight, s.norm_eps, 1.0 - s.difference, x.dtype)
         return self.out(o)
