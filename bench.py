@@ -4,7 +4,7 @@ B200, bfloat16, through the engine's own step function; prefill of 2,048 tokens;
 and 64; the same decode measured end to end through the Python entry point.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
-    python bench.py --design duduvik|nipizen|lugipel [--size small|medium|large]     (another workload; see the option's help)
+    python bench.py --design duduvik|nipizen|lugipel|folavik [--size small|medium|large]     (another workload; see the option's help)
 
 One JSON line goes to standard output.  `value` is decoded tokens per second at batch 8 with contexts
 of the configuration's benchmark length, timed on the device with CUDA events around K decode steps
@@ -580,7 +580,7 @@ def main() -> int:
                         help="no measurement: print every kernel of one decode step (default: the headline's batch and context) "
                              "with its start, length and its share of the critical path inside the replayed graph (CUPTI "
                              "through torch.profiler), and exit")
-    parser.add_argument("--design", choices=["duduvik", "nipizen", "lugipel"], default=None,
+    parser.add_argument("--design", choices=["duduvik", "nipizen", "lugipel", "folavik"], default=None,
                         help="instead of the headline record: prefill and decode throughput of that design at layer sizes that "
                              "resemble a real model's, beside the engine's closest other design at equal width and depth (random weights), one "
                              "JSON line each, and the design's kernels by their share of a step")

@@ -1,9 +1,9 @@
 """
 Prefill and decode throughput of a design at layer sizes that resemble a real model's, beside the
 engine's closest other design at equal width and depth (Duduvik beside Llama, Nipizen beside
-Duduvik, Lugipel beside Nipizen), both with random weights through the engine's own step function:
+Duduvik, Lugipel beside Nipizen, Folavik beside Llama), both with random weights through the engine's own step function:
 
-    python bench.py --design duduvik|nipizen|lugipel [--size small|medium|large] [--steps K] [--warmup W]
+    python bench.py --design duduvik|nipizen|lugipel|folavik [--size small|medium|large] [--steps K] [--warmup W]
 
 For each design: a prompt of `prefill` tokens in one step (launched kernel by kernel), and decode
 steps of `batch` requests at `context` tokens each (replayed from a CUDA graph), timed on the device
@@ -89,6 +89,34 @@ def lugipel_config(s: dict) -> dict:
     layers = [dict(gru, mlp=dense) if i % 3 == 1 else dict(att, mlp=moe) for i in range(s["layers"])]
     return {"architecture": "Lugipel", "vocab": VOCAB, "width": width, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-6},
             "layers": layers}
+
+
+def folavik_config(s: dict) -> dict:
+    """
+    Layers in the order differential attention / latent attention / chunked attention, every one with a dense
+    gelu-gated feed-forward of the Llama model's width.  Heads of 128 channels for keys and values, so that the
+    tensor-core attention kernels take them: the chunked layers with 4 query heads a key/value head, chunks of
+    1,024 tokens and rotation over half a head; the differential layers with half as many heads of two maps each
+    (as many score maps as the other layers have heads), a window of 1,024 tokens, scores capped at 50; the latent
+    layers with a latent of 512 channels.
+    """
+    width, heads = s["width"], s["heads"]
+    dim = width // heads                                   # 128 at every size
+    diff = {"type": "attention_2",
+            "mixer": {"heads": heads // 2, "kv_heads": max(1, heads // 8), "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                      "mask": {"size": 1024}, "softcap": 50.0, "diff": 0.6,
+                      "rot": {"base": 250000.0, "dims": dim // 2,
+                              "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    lat = {"type": "latent_attention", "mixer": {"heads": heads, "dim": dim, "vdim": dim, "kv_rank": 512, "scale": dim ** -0.5}}
+    att = {"type": "attention",
+           "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                     "mask": {"size": 1024},
+                     "rot": {"base": 500000.0, "dims": dim // 2,
+                             "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    dense = {"kind": "dense", "ff": s["ff"]}
+    mixers = (diff, lat, att)
+    return {"architecture": "Folavik", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
+            "logit_softcap": 30.0, "layers": [dict(mixers[i % 3], mlp=dense) for i in range(s["layers"])]}
 
 
 def llama_config(s: dict) -> dict:
@@ -222,8 +250,10 @@ def run(design: str, size: str, steps: int, warmup: int, peaks: dict) -> int:
         pair = (("duduvik", duduvik_config(s), True), ("nipizen", nipizen_config(s), True))
     elif design == "lugipel":
         pair = (("nipizen", nipizen_config(s), True), ("lugipel", lugipel_config(s), True))
+    elif design == "folavik":
+        pair = (("llama", llama_config(s), True), ("folavik", folavik_config(s), True))
     else:
-        raise SystemExit(f"--design {design!r}: have ['duduvik', 'nipizen', 'lugipel']")
+        raise SystemExit(f"--design {design!r}: have ['duduvik', 'nipizen', 'lugipel', 'folavik']")
     for name, cfg, profile in pair:
         record = {"design": name, "size": size, "width": s["width"], "layers": s["layers"], "dtype": "bf16",
                   "data": "synthetic", "timing": "CUDA events, median, L2 flushed between timed steps", "peaks": peaks}
