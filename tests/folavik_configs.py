@@ -76,12 +76,14 @@ WIDE = model(512, 128, 1e-6, 2.0, 20.0, [
     (chunked(4, 2, 64, 64, 0.15, 96, 64, 500000.0, bands=(8.0, 1.0, 4.0, 128)), dense(128)),
     (latent(4, 32, 48, 64, 0.18), dense(96)),
     (chunked(2, 1, 64, 64, 0.12, 200, 16, 1000.0), None),
+    (latent(2, 64, 64, 96, 0.2), dense(64)),
 ])
 
 # heads of 128 channels for keys and values, three query heads a key/value head
 GROUPED = model(257, 128, 1e-5, 1.0, 12.0, [
     (differential(3, 1, 128, 128, 0.09, 70, 64, 10000.0, 0.4, 20.0), dense(64)),
     (chunked(6, 2, 128, 128, 0.08, 130, 128, 100000.0, bands=(2.0, 1.0, 2.0, 64)), dense(96)),
+    (latent(3, 128, 128, 160, 0.1), None),
 ])
 
 WEIGHTS = {"std": 0.08, "unit_std": 0.25}

@@ -192,6 +192,28 @@ def test_latent_attention_without_positions(dtype, heads, dim, vdim, rank, page)
     _compare_in_steps(mixer, w, dtype, width, lambda x: plain.latent_attention(x, w, m, 1e-5), page=page)
 
 
+@pytest.mark.parametrize("heads, dim, rank, page", [(4, 64, 96, 16), (2, 128, 40, 64), (5, 64, 512, 64)])
+def test_latent_attention_of_long_portions_on_keys_and_values_worked_out_for_the_step(heads, dim, rank, page):
+    """
+    bfloat16, key and value heads of one size the tcgen05 prompt kernel takes: portions of 128 tokens and more attend
+    over keys and values worked out from the gathered latents of the whole context (a cached prefix included),
+    beside a request that feeds one token in the same step, which stays on the folded form; shorter steps before
+    and after run the folded form alone.
+    """
+    from tinyserve_llm_b200.config.spec import LatentAttentionSpec
+    dtype, width = torch.bfloat16, 64
+    spec = LatentAttentionSpec(hidden_size=width, num_heads=heads, head_dim=dim, rot_dim=0, value_dim=dim, q_rank=0, kv_rank=rank,
+                               scale=0.2, norm_eps=1e-5, position=None, output_gate=True)
+    mixer, w = _mixer(spec, dtype, 11)
+    m = {"heads": heads, "dim": dim, "vdim": dim, "kv_rank": rank, "scale": 0.2}
+    lens = [400, 150]
+    cuts = [[(0, 200), (0, 3)], [(200, 201), (3, 140)], [(201, 400), (140, 150)]]
+    calls = mixer.rt.ops.calls
+    before = calls.get("ts_prefill_attention_tcgen05_dense", 0), calls.get("ts_latent_attention", 0)
+    _compare_in_steps(mixer, w, dtype, width, lambda x: plain.latent_attention(x, w, m, 1e-5), page=page, lens=lens, cuts=cuts)
+    assert calls.get("ts_prefill_attention_tcgen05_dense", 0) == before[0] + 3 and calls.get("ts_latent_attention", 0) == before[1] + 1
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads, kv_heads, dim, vdim, chunk, dims, bands, page", [
     (6, 2, 20, 36, 11, 12, (4.0, 2.0, 8.0, 64), 16), (3, 3, 16, 16, 16, 16, None, 16), (2, 1, 32, 64, 1, 8, None, 16),

@@ -255,7 +255,8 @@ def _ctx(ranges):
     return SimpleNamespace(positions=_i32(positions), seq_of_token=_i32(seqs), cu_q=_i32(cu), ctx_lens=_i32([b for _, b in ranges]),
                            max_q_len=max(lens), min_q_len=min(lens), max_ctx_len=max(b for _, b in ranges),
                            max_decode_ctx_len=max([b for a, b in ranges if b - a == 1], default=0), scratch={},
-                           prefill_seqs=_i32([s for s, n in enumerate(lens) if n > 1]), num_tokens=sum(lens))
+                           prefill_seqs=_i32([s for s, n in enumerate(lens) if n > 1]), num_tokens=sum(lens), replayed=False,
+                           host=SimpleNamespace(cu_q=cu, ctx_lens=[b for _, b in ranges], start=[a for a, _ in ranges]))
 
 
 class _Slots:

@@ -216,6 +216,8 @@ struct FlashParams {
     int chunk;                        // n > 0: a query sees no key before floor(p / n) * n
     float cap_pre;                    // scores are capped: tanh(product * cap_pre), and scale_log2 is cap * log2(e); 0: not capped
     int value_heads;                  // heads of the value pool (a divisor of nkv)
+    // keys and values in matrices of their own instead of pages: [rows, nkv * HD], request s's key j in row kv_start[s] + j
+    const int* kv_start;              // null: keys and values come from the paged pools
 };
 
 // SIG: a visible key's weight is sigmoid(score * scale - slope (position - key) + bias): no maximum, no sum, no
@@ -264,6 +266,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
     const int nv = LOW ? p.value_heads : p.nkv, vh = LOW ? kvh / (p.nkv / p.value_heads) : kvh;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* table = p.block_table + (long long)seq * p.table_width;
+    const int dense_row0 = p.kv_start ? p.kv_start[seq] : -1;
 
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_tile = base;
@@ -308,14 +311,21 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
 #pragma unroll
             for (int b = 0; b < KEYS / 64; ++b) {    // boxes of 64 keys x 64 dims: a box never crosses a page
                 const int key = j * KEYS + b * 64;
-                int page = table[min(key / p.page_tokens, p.table_width - 1)];
-                if (page < 0 || page >= p.num_pages) page = 0;     // given back or beyond the request: masked anyway
-                const int row = ((page * p.entries + p.entry) * p.nkv + kvh) * p.page_tokens + key % p.page_tokens;
-                const int v_row = ((page * p.entries + p.entry) * nv + vh) * p.page_tokens + key % p.page_tokens;
+                int row, v_row, col = 0, v_col = 0;
+                if (dense_row0 >= 0) {               // rows past the request's last key belong to the next request, or to nobody
+                    row = v_row = dense_row0 + key;  // (the copy fills those with zeros): masked anyway
+                    col = kvh * HD;
+                    v_col = vh * HD;
+                } else {
+                    int page = table[min(key / p.page_tokens, p.table_width - 1)];
+                    if (page < 0 || page >= p.num_pages) page = 0;     // given back or beyond the request: masked anyway
+                    row = ((page * p.entries + p.entry) * p.nkv + kvh) * p.page_tokens + key % p.page_tokens;
+                    v_row = ((page * p.entries + p.entry) * nv + vh) * p.page_tokens + key % p.page_tokens;
+                }
 #pragma unroll
                 for (int h = 0; h < SUBS; ++h) {
-                    tma_load_2d(k_tile + h * SUB_KV + b * (64 * 128), &map_k, &kv_full[s], h * 64, row);
-                    tma_load_2d(v_tile + h * SUB_KV + b * (64 * 128), &map_v, &kv_full[s], h * 64, v_row);
+                    tma_load_2d(k_tile + h * SUB_KV + b * (64 * 128), &map_k, &kv_full[s], col + h * 64, row);
+                    tma_load_2d(v_tile + h * SUB_KV + b * (64 * 128), &map_v, &kv_full[s], v_col + h * 64, v_row);
                 }
             }
         }
@@ -638,7 +648,8 @@ int run_prefill(const void* q, long long q_cols, long long q_stride, void* out, 
                 const int* cu_q, const int* ctx_lens, int num_seqs, int num_tokens, int max_q_len, int nh, int nkv, int hd,
                 float scale, const int* prefill_seqs, int num_prefill_seqs, int* error, bool sigmoid, int window,
                 const float* slopes, const float* head_bias, const void* gate, long long gate_stride, cudaStream_t stream,
-                bool bounded = false, int chunk = 0, float softcap = 0.f, int value_heads = 0) {
+                bool bounded = false, int chunk = 0, float softcap = 0.f, int value_heads = 0, const int* kv_start = nullptr,
+                long long dense_rows = 0) {
     TS_REQUIRE(ts_attention_tcgen05_supported(hd, page_tokens, nh, nkv, 0), "attention_tcgen05: sizes not taken (head_dim %d, page %d)", hd, page_tokens);
     TS_REQUIRE(sigmoid || bounded || window == 0, "attention_tcgen05: the plain form takes no window");
     TS_REQUIRE(window >= 0 && chunk >= 0 && softcap >= 0.f, "attention_tcgen05: a negative window, chunk or cap");
@@ -657,8 +668,14 @@ int run_prefill(const void* q, long long q_cols, long long q_stride, void* out, 
     TS_REQUIRE(pool_rows < 0x7fffffffll, "attention_tcgen05: the pool has too many rows for 32-bit TMA coordinates");
     CUtensorMap map_q, map_k, map_v;
     if (make_map(&map_q, q, num_tokens, q_cols, q_stride, QROWS)) return 1;
-    if (make_map(&map_k, k_pool, pool_rows, hd, hd, 64)) return 1;
-    if (make_map(&map_v, v_pool, pool_rows / nkv * value_heads, hd, hd, 64)) return 1;
+    if (kv_start != nullptr) {                           // matrices [dense_rows, heads * hd]
+        TS_REQUIRE(dense_rows > 0 && dense_rows < 0x7fffffffll, "attention_tcgen05: %lld rows of keys", dense_rows);
+        if (make_map(&map_k, k_pool, dense_rows, (long long)nkv * hd, (long long)nkv * hd, 64)) return 1;
+        if (make_map(&map_v, v_pool, dense_rows, (long long)value_heads * hd, (long long)value_heads * hd, 64)) return 1;
+    } else {
+        if (make_map(&map_k, k_pool, pool_rows, hd, hd, 64)) return 1;
+        if (make_map(&map_v, v_pool, pool_rows / nkv * value_heads, hd, hd, 64)) return 1;
+    }
     FlashParams p;
     p.out = (__nv_bfloat16*)out;
     p.block_table = block_table;
@@ -676,6 +693,7 @@ int run_prefill(const void* q, long long q_cols, long long q_stride, void* out, 
     p.cap_pre = softcap > 0.f ? scale / softcap : 0.f;
     p.chunk = chunk;
     p.value_heads = value_heads;
+    p.kv_start = kv_start;
     p.error = error;
     p.window = window;
     p.slopes = slopes;
@@ -748,4 +766,19 @@ TS_API int ts_prefill_attention_tcgen05_masked(const void* q, long long q_stride
                        block_table, table_width, cu_q, ctx_lens, num_seqs, num_tokens, max_q_len, nh, nkv, hd, scale,
                        prefill_seqs, num_prefill_seqs, error, false, window, nullptr, nullptr, nullptr, 0, stream, true, chunk,
                        softcap, value_heads);
+}
+
+// Causal softmax attention of prompt portions over keys and values that lie in matrices of their own,
+// k [kv_rows, nkv * hd] and v [kv_rows, nkv * hd] (bfloat16, rows back to back), request s's key j in row kv_start[s] + j
+// (kv_start: int32 [num_seqs] on the device; ctx_lens[s] keys a request).  For keys and values that are worked out
+// for the step instead of read from pages.  Queries [T, nh * hd] in a matrix of their own, q_stride elements a row.
+TS_API int ts_prefill_attention_tcgen05_dense(const void* q, long long q_stride, void* out, const void* k, const void* v,
+                                              long long kv_rows, const int* kv_start, const int* cu_q, const int* ctx_lens,
+                                              int num_seqs, int num_tokens, int max_q_len, int nh, int nkv, int hd,
+                                              float scale, const int* prefill_seqs, int num_prefill_seqs, int* error,
+                                              cudaStream_t stream) {
+    TS_REQUIRE(kv_start != nullptr, "attention_tcgen05: the first rows of the requests' keys are needed");
+    return run_prefill(q, (long long)nh * hd, q_stride, out, k, v, 1, 1, 0, 64, nullptr, 1, cu_q, ctx_lens, num_seqs, num_tokens,
+                       max_q_len, nh, nkv, hd, scale, prefill_seqs, num_prefill_seqs, error, false, 0, nullptr, nullptr,
+                       nullptr, 0, stream, false, 0, 0.f, 0, kv_start, kv_rows);
 }

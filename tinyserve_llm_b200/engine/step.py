@@ -70,6 +70,9 @@ class StepContext:
         # the split-key decode kernels size their grid and scratch by the longest request that feeds one token
         self.max_decode_ctx_len = max((c for c, n in zip(host.ctx_lens, lens) if n == 1), default=0)
         self.scratch: dict = {}                   # per-step scratch buffers parts share (keyed by purpose and size)
+        # True: the step is captured into a CUDA graph or replayed from one, so a part must launch the same kernels on
+        # buffers of the same sizes whatever the step holds; False: it runs once, and `host` says exactly what it holds
+        self.replayed = False
 
     def binding(self, entry: RunEntry) -> EntryBinding | None:
         base = self._runner.bindings[entry.cache_entry]
@@ -325,6 +328,7 @@ class StepRunner:
                         ctx_lens[:n], sizes["slots"][:n])
         ctx = StepContext(self, sizes["tokens"], sizes["seqs"], host)
         ctx.index_words = len(words)
+        ctx.replayed = shape is not None
         if shape is not None:                     # a graph is replayed for any step its shape can hold
             bound = max(w * self.manager.page_tokens for w in shape.widths) if shape.widths else 0
             ctx.max_q_len, ctx.min_q_len = shape.max_q, (1 if shape.decodes else shape.max_q)

@@ -32,6 +32,7 @@ _SIGNATURES = {
     "ts_paged_attention_bf16_sigmoid": ("int", "pl" "ppp" "lliipippiiiiiiifiplpi" "pppl" "p"),
     "ts_paged_attention_bf16_masked": ("int", "pl" "ppp" "lllliipippiiiiiiifiifi" "plpi" "p"),
     "ts_attention_tcgen05_supported": ("int", "iiiii"),
+    "ts_prefill_attention_tcgen05_dense": ("int", "pl" "ppp" "lpppiiiiiifpipp"),
     "ts_prefill_attention_tcgen05_masked": ("int", "pl" "ppp" "iiiipippiiiiiifiifi" "pipp"),
     "ts_prefill_attention_tcgen05": ("int", "ppppiiiipippiiiiiifpipp"),
     "ts_prefill_attention_tcgen05_sigmoid": ("int", "pl" "ppp" "iiiipippiiiiiifi" "pppl" "pipp"),
@@ -733,6 +734,38 @@ class Ops:
                    1 if weights == "sigmoid" else 0, _ptr(slopes), _ptr(head_bias), _ptr(head_gate),
                    head_gate.stride(0) if head_gate is not None else 0, float(softcap), int(chunk), int(value_heads),
                    1 if out_f32 else 0, _stream())
+        return out
+
+    def dense_prompt_attention_supported(self, q: torch.Tensor, nh: int, nkv: int, hd: int) -> bool:
+        """Whether `dense_prompt_attention` takes these sizes (bfloat16, heads of 64 or 128 channels, aligned query rows)."""
+        return bool(q.dtype == torch.bfloat16 and q.dim() == 2 and q.stride(1) == 1 and q.stride(0) % 8 == 0
+                    and q.data_ptr() % 16 == 0 and self.tcgen05_attention
+                    and self.lib.ts_attention_tcgen05_supported(hd, 64, nh, nkv, 0))
+
+    def dense_prompt_attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_start: torch.Tensor, ctx, nh: int,
+                               nkv: int, hd: int, scale: float, out: torch.Tensor | None = None) -> torch.Tensor:
+        """
+        Causal softmax attention of the step's prompt portions (requests that feed more than one token) over keys
+        and values worked out for the step: k, v [rows, nkv * hd] bfloat16, request s's key j in row kv_start[s] + j
+        (int32 [requests] on the device), ctx.ctx_lens[s] keys a request.  Rows of requests that feed one token are
+        left as they are in `out` ([T, nh * hd]; made here if not given).  The tcgen05 prompt kernel.
+        """
+        self._check_rows(q, "q")
+        self._check(k, "k", torch.bfloat16, 2)
+        self._check(v, "v", torch.bfloat16, 2)
+        self._check(kv_start, "kv_start", torch.int32, 1)
+        if k.shape != v.shape or k.shape[1] != nkv * hd or q.shape[1] != nh * hd or kv_start.shape[0] != ctx.ctx_lens.shape[0]:
+            raise KernelError(f"dense_prompt_attention: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)} for "
+                              f"{nh}:{nkv} heads of {hd}")
+        if not self.dense_prompt_attention_supported(q, nh, nkv, hd):
+            raise KernelError(f"dense_prompt_attention: sizes not taken ({nh}:{nkv} heads of {hd}, {q.dtype})")
+        if out is None:
+            out = torch.empty((q.shape[0], nh * hd), dtype=q.dtype, device=q.device)
+        prefill_seqs = getattr(ctx, "prefill_seqs", None)
+        num_prefill = prefill_seqs.shape[0] if prefill_seqs is not None else 0
+        self._call("ts_prefill_attention_tcgen05_dense", _ptr(q), q.stride(0), _ptr(out), _ptr(k), _ptr(v), k.shape[0],
+                   _ptr(kv_start), _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), ctx.ctx_lens.shape[0], q.shape[0], ctx.max_q_len, nh, nkv,
+                   hd, scale, _ptr(prefill_seqs), num_prefill, self.error_word().data_ptr(), _stream())
         return out
 
     def tensor_core_attention(self, q: torch.Tensor, binding, nh: int, nkv: int, hd: int, vd: int, ctx=None) -> bool:

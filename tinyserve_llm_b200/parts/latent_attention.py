@@ -17,6 +17,13 @@ latent and a norm of their own; `rot_dim` 0 leaves out the rotated part (attenti
 cache row is c alone and no position part is built); `output_gate` multiplies the concatenated heads by
 sigmoid(W_g h), read from the same input as the other projections, before W_o.
 
+Prompt portions of a step that is launched once (not replayed from a CUDA graph) take another way where the
+sizes allow (bfloat16, no rotated part, key and value heads of one size the tcgen05 prompt kernel takes): the
+latents of the requests' whole contexts are gathered from the pages, a head's keys and values are worked out
+for the step (K = C W_uk^T, V = C W_uv^T, two library products: a quarter of the folded form's arithmetic at
+a latent of 512 channels and heads of 128) and the tcgen05 prompt kernel attends over them; requests that feed
+one token in the same step stay on the folded form.  The two ways differ by rounding only.
+
 Tensors (local names): dq, dq.norm, uq (or q), dkv, dkv.norm, uk, uv, o, and g with an output gate.
 """
 
@@ -29,6 +36,7 @@ from tinyserve_llm_b200.parts.base import KVNeed, Mixer, Runtime, TensorDecl, pa
 from tinyserve_llm_b200.parts.linear import Linear, fuse_rows
 
 MAX_KV_RANK = 512       # csrc/attention_latent.cu: 16 output channels a lane
+MATERIALIZE_MIN_TOKENS = 128    # prompt portions of a step, together, from which keys and values are worked out for the step
 
 
 @register_part("mixer", "latent_attention")
@@ -77,6 +85,8 @@ class LatentAttention(Mixer):
         # W_uk per head, transposed to [H, rank, D]: the product that folds it into the query reads rows of D
         self.uk_t = tensors["uk"].to(device=rt.device, dtype=rt.dtype).view(H, D, rank).transpose(1, 2).contiguous()
         self.uv = tensors["uv"].to(device=rt.device, dtype=rt.dtype).view(H, V, rank).contiguous()
+        # the unfolded form of prompt portions: W_uk as stored, [H D, rank] (W_uv's stored form is self.uv's memory)
+        self.uk = self.uk_t.transpose(1, 2).reshape(H * D, rank).contiguous() if spec.rot_dim == 0 and D == V else None
         self.out = Linear(tensors["o"], rt)
         self.position = self.frequencies = None
         if spec.position is not None:
@@ -88,6 +98,46 @@ class LatentAttention(Mixer):
 
     def kv_need(self) -> KVNeed:
         return KVNeed(1, self.spec.kv_rank + self.spec.rot_dim, self.spec.window, values=False)
+
+    # ------------------------------------------------------------------ prompt portions on keys and values of their own
+    def _portions(self, q: torch.Tensor, ctx) -> list[int] | None:
+        """The step's requests that feed more than one token, if their attention is to run on keys and values worked out for the step."""
+        spec, host = self.spec, getattr(ctx, "host", None)
+        if (self.uk is None or spec.window or getattr(ctx, "replayed", True) or host is None or ctx.max_q_len <= 1
+                or not self.rt.ops.dense_prompt_attention_supported(q, spec.num_heads, spec.num_heads, spec.head_dim)):
+            return None
+        lens = [b - a for a, b in zip(host.cu_q, host.cu_q[1:])]
+        portions = [s for s, n in enumerate(lens) if n > 1]
+        if sum(lens[s] for s in portions) < MATERIALIZE_MIN_TOKENS:
+            return None
+        return portions
+
+    @staticmethod
+    def _single_tokens_only(ctx):
+        """The step's context with the tokens of prompt portions marked as padding rows: the folded form skips them."""
+        import copy
+        lens = ctx.cu_q[1:] - ctx.cu_q[:-1]
+        seqs = ctx.seq_of_token.long().clamp_min(0)
+        out = copy.copy(ctx)
+        out.seq_of_token = torch.where((ctx.seq_of_token >= 0) & (lens[seqs] == 1), ctx.seq_of_token, -1).to(torch.int32)
+        return out
+
+    def _attend_unfolded(self, q: torch.Tensor, ctx, binding, portions: list[int], out: torch.Tensor | None) -> torch.Tensor:
+        spec, ops, host = self.spec, self.rt.ops, ctx.host
+        H, D, rank, B = spec.num_heads, spec.head_dim, spec.kv_rank, binding.page_tokens
+        entries = binding.page_stride // (B * rank)
+        pool = binding.k_pool.view(binding.num_pages, entries, B, rank)[:, binding.entry_offset // (B * rank)]
+        starts, latents, at = [0] * len(host.ctx_lens), [], 0
+        for s in portions:                                  # the latents of the whole context, page by page
+            n = host.ctx_lens[s]
+            pages = binding.block_table[s, :-(-n // B)].long()
+            latents.append(pool[pages].reshape(-1, rank)[:n])
+            starts[s], at = at, at + n
+        c = torch.cat(latents) if len(latents) > 1 else latents[0].contiguous()
+        kv_start = torch.tensor(starts, dtype=torch.int32).to(q.device, non_blocking=True)
+        k = ops.linear(c, self.uk)                          # [keys, H D]
+        v = ops.linear(c, self.uv.view(H * spec.value_dim, rank))
+        return ops.dense_prompt_attention(q, k, v, kv_start, ctx, H, H, D, spec.scale, out)
 
     def forward(self, x: torch.Tensor, ctx, binding) -> torch.Tensor:
         spec, ops = self.spec, self.rt.ops
@@ -103,11 +153,18 @@ class LatentAttention(Mixer):
             q = y[:, :H * (D + R)]
             ops.latent_prepare(y[:, H * (D + R):latents], ctx, binding, 0, rank, R, None, self.kv_norm, spec.norm_eps,
                                self.frequencies)
-        q_lat = ops.per_head_linear(q, self.uk_t, H, D + R, D)            # float32 [T, H, rank]: W_uk^T q_flat
-        o_lat = ops.latent_attention(q_lat, q, ctx, binding, H, D + R, D, rank, R, self.frequencies,
-                                     spec.scale, spec.window)             # [T, H, rank]: softmax-weighted sums of c
-        o = ops.per_head_linear(o_lat.view(-1, H * rank), self.uv, H, rank, rank, out_dtype=x.dtype)   # [T, H, V]
-        o = o.reshape(-1, H * V)
+        portions = self._portions(q, ctx)
+        if portions is not None and ctx.min_q_len > 1:
+            o = self._attend_unfolded(q, ctx, binding, portions, None)
+        else:
+            folded_ctx = ctx if portions is None else self._single_tokens_only(ctx)
+            q_lat = ops.per_head_linear(q, self.uk_t, H, D + R, D)        # float32 [T, H, rank]: W_uk^T q_flat
+            o_lat = ops.latent_attention(q_lat, q, folded_ctx, binding, H, D + R, D, rank, R, self.frequencies,
+                                         spec.scale, spec.window)         # [T, H, rank]: softmax-weighted sums of c
+            o = ops.per_head_linear(o_lat.view(-1, H * rank), self.uv, H, rank, rank, out_dtype=x.dtype)   # [T, H, V]
+            o = o.reshape(-1, H * V)
+            if portions is not None:                                      # the portions' rows are written over
+                o = self._attend_unfolded(q, ctx, binding, portions, o.contiguous())
         if spec.output_gate:
             o = ops.sigmoid_gate(o, y[:, latents:latents + H * V])
         return self.out(o)
