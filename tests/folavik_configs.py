@@ -58,7 +58,7 @@ EDGES = model(128, 80, 1e-6, 1.0, None, [
     (differential(5, 5, 12, 20, 0.4, 1000, 4, 100.0, 0.3, 5.0, yarn=(2.0, 32, 8.0, 1.0)), dense(96)),
     (chunked(2, 1, 32, 64, 0.15, 1, 8, 10000.0), dense(40)),
     (differential(1, 1, 24, 12, 0.2, 1, 24, 700.0, 0.5, 30.0), dense(33)),
-    (chunked(4, 4, 8, 8, 0.35, 1000, 8, 50.0, bands=(8.0, 1.0, 4.0, 32)), None),
+    (chunked(4, 4, 8, 8, 0.35, 1000, 8, 50.0, bands=(5.0, 1.0, 3.0, 32)), None),
     (latent(1, 16, 16, 8, 0.25), dense(20)),
 ])
 
@@ -72,8 +72,8 @@ LATENT = model(211, 64, 1e-5, 0.5, 30.0, [
 # of 32, keys and values of 64 channels a head on pages of 64 tokens, a latent of 64 channels); masks that end
 # inside pages and inside the kernels' tiles of 64 and 128 keys
 WIDE = model(512, 128, 1e-6, 2.0, 20.0, [
-    (differential(4, 2, 64, 64, 0.125, 80, 32, 250000.0, 0.6, 30.0, yarn=(4.0, 128, 32.0, 1.0)), dense(192)),
-    (chunked(4, 2, 64, 64, 0.15, 96, 64, 500000.0, bands=(8.0, 1.0, 4.0, 128)), dense(128)),
+    (differential(4, 2, 64, 64, 0.125, 80, 32, 130000.0, 0.45, 25.0, yarn=(3.0, 128, 24.0, 1.5)), dense(192)),
+    (chunked(4, 2, 64, 64, 0.15, 96, 64, 300000.0, bands=(6.0, 1.0, 3.0, 128)), dense(128)),
     (latent(4, 32, 48, 64, 0.18), dense(96)),
     (chunked(2, 1, 64, 64, 0.12, 200, 16, 1000.0), None),
     (latent(2, 64, 64, 96, 0.2), dense(64)),

@@ -175,7 +175,7 @@ def _compare_in_steps(mixer, w, dtype, width, want_of, page=16, lens=LENS, cuts=
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads, dim, vdim, rank, page", [(5, 24, 20, 40, 16), (1, 16, 16, 8, 16), (4, 32, 48, 64, 64), (3, 8, 72, 96, 16),
+@pytest.mark.parametrize("heads, dim, vdim, rank, page", [(5, 24, 20, 40, 16), (1, 16, 16, 8, 16), (4, 32, 48, 64, 64), (3, 8, 72, 96, 16), (3, 12, 10, 20, 16),
                                                           (16, 64, 64, 128, 64), (2, 48, 56, 24, 16)])
 def test_latent_attention_without_positions(dtype, heads, dim, vdim, rank, page):
     """
@@ -217,7 +217,7 @@ def test_latent_attention_of_long_portions_on_keys_and_values_worked_out_for_the
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads, kv_heads, dim, vdim, chunk, dims, bands, page", [
     (6, 2, 20, 36, 11, 12, (4.0, 2.0, 8.0, 64), 16), (3, 3, 16, 16, 16, 16, None, 16), (2, 1, 32, 64, 1, 8, None, 16),
-    (4, 2, 64, 64, 96, 64, (8.0, 1.0, 4.0, 128), 64), (6, 2, 128, 128, 50, 32, None, 64), (4, 4, 64, 64, 1000, 16, None, 64),
+    (4, 2, 64, 64, 96, 64, (6.0, 1.0, 3.0, 128), 64), (6, 2, 128, 128, 50, 32, None, 64), (4, 4, 64, 64, 1000, 16, None, 64),
     (2, 1, 64, 64, 64, 64, None, 64)])
 def test_chunked_attention_alone(dtype, heads, kv_heads, dim, vdim, chunk, dims, bands, page):
     """
@@ -239,7 +239,7 @@ def test_chunked_attention_alone(dtype, heads, kv_heads, dim, vdim, chunk, dims,
 @pytest.mark.parametrize("heads, kv_heads, dim, vdim, window, dims, yarn, cap, diff, page", [
     (4, 2, 16, 24, 37, 6, (4.0, 64, 16.0, 2.0), 12.0, 0.55, 16), (3, 1, 40, 8, 9, 40, None, 50.0, 0.8, 16),
     (5, 5, 12, 20, 1000, 4, (2.0, 32, 8.0, 1.0), 5.0, 0.3, 16), (1, 1, 24, 12, 1, 24, None, 30.0, 0.5, 16),
-    (4, 2, 64, 64, 80, 32, (4.0, 128, 32.0, 1.0), 30.0, 0.6, 64), (3, 1, 128, 128, 70, 64, None, 20.0, 0.4, 64),
+    (4, 2, 64, 64, 80, 32, (3.0, 128, 24.0, 1.5), 25.0, 0.45, 64), (3, 1, 128, 128, 70, 64, None, 20.0, 0.4, 64),
     (2, 2, 64, 64, 64, 8, None, 2.0, 0.2, 64), (8, 2, 64, 64, 129, 64, None, 0.0, 0.1, 64)])
 def test_differential_attention_alone(dtype, heads, kv_heads, dim, vdim, window, dims, yarn, cap, diff, page):
     """

@@ -116,8 +116,8 @@ def test_maps_are_grouped_by_key_head():
     assert torch.equal(group_maps_together(rows[:, 0].contiguous(), heads, kv_heads, dim), out[:, 0])
 
 
-@pytest.mark.parametrize("dims, base, bands", [(64, 500000.0, (8.0, 1.0, 4.0, 512)), (16, 10000.0, (4.0, 2.0, 8.0, 64)),
-                                               (12, 5000.0, (4.0, 2.0, 8.0, 64)), (8, 50.0, (8.0, 1.0, 4.0, 32))])
+@pytest.mark.parametrize("dims, base, bands", [(64, 400000.0, (6.0, 1.0, 5.0, 384)), (16, 10000.0, (4.0, 2.0, 8.0, 64)),
+                                               (12, 5000.0, (4.0, 2.0, 8.0, 64)), (8, 50.0, (5.0, 1.0, 3.0, 32))])
 def test_frequencies_rescaled_by_wavelength_bands(dims, base, bands):
     """Kept, slowed and blended frequencies all occur in the first case; the engine's table equals the plain one's."""
     from tinyserve_llm_b200.config.spec import Llama3Scaling
@@ -135,7 +135,7 @@ def test_frequencies_rescaled_by_wavelength_bands(dims, base, bands):
 def test_yarn_frequencies_and_magnitude():
     from tinyserve_llm_b200.config.spec import YarnScaling
     from tinyserve_llm_b200.parts.rotary import yarn_frequencies
-    for dims, base, yarn in ((8, 250000.0, (4.0, 512, 32.0, 1.0)), (40, 20000.0, (2.0, 32, 8.0, 1.0)), (6, 900.0, (4.0, 64, 16.0, 2.0))):
+    for dims, base, yarn in ((8, 150000.0, (3.0, 256, 24.0, 1.5)), (40, 20000.0, (2.0, 32, 8.0, 1.0)), (6, 900.0, (4.0, 64, 16.0, 2.0))):
         sc = dict(zip(("factor", "original", "fast", "slow"), yarn))
         want, magnitude = plain.yarn_frequencies(dims, base, sc)
         got = yarn_frequencies(dims, base, YarnScaling(*yarn))

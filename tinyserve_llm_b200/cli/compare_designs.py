@@ -104,9 +104,9 @@ def folavik_config(s: dict) -> dict:
     dim = width // heads                                   # 128 at every size
     diff = {"type": "attention_2",
             "mixer": {"heads": heads // 2, "kv_heads": max(1, heads // 8), "dim": dim, "vdim": dim, "scale": dim ** -0.5,
-                      "mask": {"size": 1024}, "softcap": 50.0, "diff": 0.6,
-                      "rot": {"base": 250000.0, "dims": dim // 2,
-                              "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+                      "mask": {"size": 1024}, "softcap": 50.0, "diff": 0.5,
+                      "rot": {"base": 1000000.0, "dims": dim // 2,
+                              "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}}
     lat = {"type": "latent_attention", "mixer": {"heads": heads, "dim": dim, "vdim": dim, "kv_rank": 512, "scale": dim ** -0.5}}
     att = {"type": "attention",
            "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": dim, "vdim": dim, "scale": dim ** -0.5,
