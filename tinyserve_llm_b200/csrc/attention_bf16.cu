@@ -235,7 +235,7 @@ struct AttnParams {
     int window;
     int chunk;                 // 0: no chunks
     float cap_pre;             // CAPPED: scale / cap, what the raw product is multiplied by inside the tanh
-    int value_heads;           // heads of the value pool (a divisor of nkv)
+    int value_group;           // key heads a value head (1: as many value heads as key heads)
     KVGeometry geo_v;          // the value pool's geometry
     const int* prefill_seqs;   // requests that feed more than one token, for the prefill grid (-1: none); null: every request
     // decode only
@@ -273,7 +273,7 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
     const int pos0 = ctx - q_len + row0;                                              // position of that query
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = head / (p.nh / p.nkv);
-    const int vh = kvh / (p.nkv / p.value_heads);
+    const int vh = p.value_group == 1 ? kvh : kvh / p.value_group;
     const long long row_width = p.q_stride;
     const int* table = p.block_table + (long long)seq * p.table_width;
 
@@ -403,7 +403,7 @@ __global__ void __launch_bounds__(DW * 32) decode_attention_kernel(AttnParams p)
     int valid = 0;
     if (warp_active) {
         k_src = kv_row_of_page<HD>(p.k_pool, p.geo, page0, kvh, key0);
-        v_src = kv_row_of_page<HD>(p.v_pool, p.geo_v, page0, kvh / (p.nkv / p.value_heads), key0);
+        v_src = kv_row_of_page<HD>(p.v_pool, p.geo_v, page0, p.value_group == 1 ? kvh : kvh / p.value_group, key0);
         valid = k_src ? min(DKT, ctx - key0) : 0;
         if (!holds_new) {
             if (k_src) {
@@ -670,7 +670,7 @@ int run(const void* q, long long q_stride, void* out, const void* k_pool, const 
     p.cap_pre = softcap > 0.f ? scale / softcap : 0.f;
     p.window = window;
     p.chunk = chunk;
-    p.value_heads = value_heads > 0 ? value_heads : nkv;
+    p.value_group = value_heads > 0 ? nkv / value_heads : 1;
     p.geo_v = v_page_stride >= 0 ? KVGeometry{v_page_stride, v_entry_offset, page_tokens, num_pages} : p.geo;
     p.max_splits = (max_ctx_len + SPLIT - 1) / SPLIT;
     p.prefill_seqs = prefill_seqs;
