@@ -86,4 +86,13 @@ GROUPED = model(257, 128, 1e-5, 1.0, 12.0, [
     (latent(3, 128, 128, 160, 0.1), None),
 ])
 
+# layer sizes that resemble a real model's: heads of 128 channels, a latent of 512, masks of 1,024 tokens across many of the
+# kernels' tiles, a width and a feed-forward the tcgen05 product with the gate in its epilogue takes
+REAL = model(2048, 1024, 1e-6, 1.0, 30.0, [
+    (differential(4, 1, 128, 128, 128 ** -0.5, 1024, 64, 1000000.0, 0.5, 50.0, yarn=(8.0, 512, 32.0, 1.0)), dense(2816)),
+    (latent(8, 128, 128, 512, 128 ** -0.5), dense(2816)),
+    (chunked(8, 2, 128, 128, 128 ** -0.5, 1024, 64, 500000.0, bands=(8.0, 1.0, 4.0, 1024)), dense(2816)),
+])
+REAL_WEIGHTS = {"std": 0.03, "unit_std": 0.1}
+
 WEIGHTS = {"std": 0.08, "unit_std": 0.25}

@@ -147,6 +147,30 @@ def test_tensor_core_sizes_also_from_graphs_token_by_token(folders):
         assert calls.get("ts_paged_attention_bf16_masked", 0) > 0 and calls.get("ts_prefill_attention_tcgen05_masked", 0) > 0
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_layer_sizes_of_a_real_model(tmp_path, dtype):
+    """
+    Three layers at a width of 1,024 with heads of 128 channels, a latent of 512 and masks of 1,024 tokens: a prompt
+    of 2,048 tokens in one step (sixteen query tiles; windows and chunks that begin many key tiles in; in bfloat16
+    the latent layer on keys and values worked out for the step and the gate in the tcgen05 product's epilogue),
+    a portion of 20 over the cached prefix, then 32 single tokens from CUDA graphs.
+    """
+    from tinyserve_llm_b200.weights import write_random_model
+    folder = str(tmp_path / "real")
+    write_random_model(folder, C.REAL, 77, **C.REAL_WEIGHTS)
+    ids = ids_of(C.REAL["vocab"], 2100, 8)
+    want = plain.forward(C.REAL, read_tensors(folder), ids)
+    eng = Engine(folder, dtype, page=64, pages=40, cuda_graphs=True)
+    got = eng.run("a", ids, [2048, 20] + [1] * 32)
+    if dtype == "float32":
+        torch.testing.assert_close(got, want, atol=2e-3, rtol=1e-3)
+        return
+    close(got, want, dtype)
+    calls = eng.model.rt.ops.calls
+    assert calls.get("ts_prefill_attention_tcgen05_dense", 0) == 1 and calls.get("ts_prefill_attention_tcgen05_masked", 0) >= 4
+    assert calls.get("ts_gemm_tcgen05_gated", 0) >= 3 and eng.runner.graph_replays >= 30
+
+
 # ---------------------------------------------------------------------------------------------- mechanisms alone
 def _rot(dims, base, yarn=None, bands=None):
     from tinyserve_llm_b200.config.spec import InlineRotarySpec, Llama3Scaling, YarnScaling
